@@ -1,0 +1,324 @@
+// All-to-all-V dispatch / combine for sm_100a with direct peer stores and loads.
+//
+// Behavioural contract of the DeepEP ElasticBuffer path the reference wraps
+// (bench_deepep.py:68-115): a token travels once to every *distinct* destination rank
+// (not once per expert), the count exchange happens inside dispatch on the device, nothing
+// synchronises with the host, and the combine returns, for each source token, the sum of
+// one row per destination rank (m * x for the identity expert).
+//
+// Design:
+//   * receive buffers are laid out [source rank][capacity][...]: a sender owns its region on
+//     every destination, so it can pick slots with a local atomic counter and push rows with
+//     plain peer stores before any count is known to the receiver;
+//   * the last block to finish publishes the per-destination row counts and arrives at a
+//     one-slot cross-GPU barrier; when the kernel has finished, every row sent to this rank
+//     is in place and recv_count[] says how many rows each source sent;
+//   * the sender remembers, per token and destination, the slot it used (slot_map); combine
+//     is a pull: after a leading barrier each warp loads its token's rows straight from the
+//     destinations' expert-output buffers, accumulates in fp32 and writes bf16;
+//   * optional 1x128 block-scaled e4m3 dispatch: amax over each 128-element block, scale =
+//     amax / 448, saturating convert, fp32 scales shipped next to the rows.
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include "mcb_barrier.cuh"
+#include "mcb_launch.h"
+
+namespace mcb {
+
+constexpr int kMaxWarps = 16;
+
+struct DestList {
+  int dst[MCB_MAX_RANKS];
+  int slot[MCB_MAX_RANKS];
+};
+
+__device__ __forceinline__ uint32_t warp_or(uint32_t v) { return __reduce_or_sync(0xffffffffu, v); }
+
+// Quantise 8 bf16 values (one 16-byte pack) with a given inverse scale to 8 e4m3 bytes.
+__device__ __forceinline__ uint2 quant_pack_e4m3(uint4 v, float inv_scale) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint16_t q[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = make_float2(bf16_lo(w[i]) * inv_scale, bf16_hi(w[i]) * inv_scale);
+    q[i] = (uint16_t)__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+  }
+  return make_uint2((uint32_t)q[0] | ((uint32_t)q[1] << 16), (uint32_t)q[2] | ((uint32_t)q[3] << 16));
+}
+
+__device__ __forceinline__ float pack_absmax(uint4 v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) m = fmaxf(m, fmaxf(fabsf(bf16_lo(w[i])), fabsf(bf16_hi(w[i]))));
+  return m;
+}
+
+template <bool EMU>
+__global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant__ McbCtx ctx_p,
+                                                           const __grid_constant__ McbA2ADispatchArgs args_p,
+                                                           const McbCtx* ectx, const McbA2ADispatchArgs* eargs) {
+  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
+  const McbA2ADispatchArgs& a = EMU ? eargs[blockIdx.y] : args_p;
+  __shared__ DestList s_list[kMaxWarps];
+  __shared__ int s_last;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int W = c.world;
+  const int epr = a.num_experts / W;
+  int n = *a.n_local;
+  if (n < 0) n = 0;
+  if (n > a.cap) {
+    if (tid == 0) report_error(c, MCB_ERR_CAPACITY, MCB_SITE_A2A_DISPATCH, blockIdx.x, (uint32_t)n, (uint32_t)a.cap);
+    n = a.cap;
+  }
+  const int row_packs = a.hidden / 8;  // 16-byte packs of bf16 per row
+  const uint8_t* x = reinterpret_cast<const uint8_t*>(a.x);
+  DestList& L = s_list[warp];
+
+  for (int t = blockIdx.x * nwarps + warp; t < n; t += gridDim.x * nwarps) {
+    // Destination ranks of this token as a bitmask (3 words cover MCB_MAX_RANKS = 72).
+    uint32_t m0 = 0, m1 = 0, m2 = 0;
+    for (int k = lane; k < a.topk; k += 32) {
+      const long long e = a.topk_idx[(long long)t * a.topk + k];
+      if (e < 0 || e >= a.num_experts) {
+        report_error(c, MCB_ERR_ROUTING, MCB_SITE_A2A_DISPATCH, blockIdx.x, (uint32_t)t, (uint32_t)e);
+        continue;
+      }
+      const int d = (int)(e / epr);
+      if (d < 32) m0 |= 1u << d; else if (d < 64) m1 |= 1u << (d - 32); else m2 |= 1u << (d - 64);
+    }
+    m0 = warp_or(m0); m1 = warp_or(m1); m2 = warp_or(m2);
+    // One slot per destination from the local counters; remember it for the combine.
+    int m = 0;
+    for (int d0 = 0; d0 < W; d0 += 32) {
+      const uint32_t word = d0 == 0 ? m0 : (d0 == 32 ? m1 : m2);
+      const int d = d0 + lane;
+      int slot = -1;
+      if (d < W && ((word >> lane) & 1u)) slot = atomicAdd(&a.send_count[d], 1);
+      if (d < W) a.slot_map[(long long)t * W + d] = slot;
+      const uint32_t have = __ballot_sync(0xffffffffu, slot >= 0);
+      if (slot >= 0) {
+        const int pos = m + __popc(have & ((1u << lane) - 1u));
+        L.dst[pos] = d;
+        L.slot[pos] = slot;
+      }
+      m += __popc(have);
+    }
+    __syncwarp();
+    const uint8_t* xrow = x + (long long)t * a.hidden * 2;
+    if (!a.fp8) {
+      const uint64_t row_bytes = (uint64_t)a.hidden * 2;
+      for (int p0 = 0; p0 < row_packs; p0 += 32 * 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int p = p0 + u * 32 + lane;
+          if (p < row_packs) v[u] = ld_v4(xrow + p * 16);
+        }
+        for (int j = 0; j < m; ++j) {
+          uint8_t* dst = c.heap_peer[L.dst[j]] + a.recv_x_off +
+                         ((uint64_t)c.rank * a.cap + L.slot[j]) * row_bytes;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int p = p0 + u * 32 + lane;
+            if (p < row_packs) st_v4(dst + p * 16, v[u]);
+          }
+        }
+      }
+    } else {
+      const int nblk = a.hidden / 128;
+      for (int p0 = 0; p0 < row_packs; p0 += 32) {
+        const int p = p0 + lane;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (p < row_packs) v = ld_v4(xrow + p * 16);
+        // amax over the 16 lanes that hold one 128-element block
+        float amax = pack_absmax(v);
+#pragma unroll
+        for (int s = 8; s >= 1; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+        const float scale = amax > 0.f ? amax * (1.0f / 448.0f) : 1.0f;
+        const uint2 q = quant_pack_e4m3(v, 1.0f / scale);
+        const int blk = p >> 4;
+        for (int j = 0; j < m; ++j) {
+          const uint64_t row = (uint64_t)c.rank * a.cap + L.slot[j];
+          uint8_t* peer = c.heap_peer[L.dst[j]];
+          if (p < row_packs) {
+            st_v2(peer + a.recv_x_off + row * a.hidden + (uint64_t)p * 8, q);
+            if ((lane & 15) == 0)
+              st_b32(peer + a.recv_scale_off + (row * nblk + blk) * 4, __float_as_uint(scale));
+          }
+        }
+      }
+    }
+    // Routing rows (ids, weights) and the source token index travel with the token.
+    for (int k = lane; k < a.topk; k += 32) {
+      const long long e = a.topk_idx[(long long)t * a.topk + k];
+      const float w = a.topk_w ? a.topk_w[(long long)t * a.topk + k] : 1.0f;
+      for (int j = 0; j < m; ++j) {
+        const uint64_t row = (uint64_t)c.rank * a.cap + L.slot[j];
+        uint8_t* peer = c.heap_peer[L.dst[j]];
+        *reinterpret_cast<long long*>(peer + a.recv_idx_off + (row * a.topk + k) * 8) = e;
+        *reinterpret_cast<float*>(peer + a.recv_w_off + (row * a.topk + k) * 4) = w;
+      }
+    }
+    if (lane == 0) {
+      for (int j = 0; j < m; ++j) {
+        const uint64_t row = (uint64_t)c.rank * a.cap + L.slot[j];
+        *reinterpret_cast<int*>(c.heap_peer[L.dst[j]] + a.recv_src_off + row * 4) = t;
+      }
+    }
+    __syncwarp();
+  }
+
+  // Grid-wide completion: the last block publishes counts and meets the other ranks.
+  __syncthreads();
+  if (tid == 0) {
+    fence_sys();
+    const int prev = atomicAdd(&a.send_count[MCB_MAX_RANKS], 1);
+    fence_sys();
+    s_last = (prev == (int)gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  const uint32_t ep = *epoch_ptr(c, MCB_SITE_A2A_DISPATCH, 0);
+  for (int d = tid; d < W; d += blockDim.x) {
+    const int cnt = atomicExch(&a.send_count[d], 0);
+    st_relaxed_sys(c.heap_peer[d] + a.recv_count_off + (uint64_t)c.rank * 4, (uint32_t)cnt);
+  }
+  if (tid == 0) a.send_count[MCB_MAX_RANKS] = 0;
+  block_barrier_all(c, MCB_SITE_A2A_DISPATCH, 0, ep);
+}
+
+template <bool EMU>
+__global__ void __launch_bounds__(512) a2a_combine_kernel(const __grid_constant__ McbCtx ctx_p,
+                                                          const __grid_constant__ McbA2ACombineArgs args_p,
+                                                          const McbCtx* ectx, const McbA2ACombineArgs* eargs) {
+  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
+  const McbA2ACombineArgs& a = EMU ? eargs[blockIdx.y] : args_p;
+  __shared__ DestList s_list[kMaxWarps];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int W = c.world;
+  int n = *a.n_local;
+  if (n < 0) n = 0;
+  if (n > a.cap) n = a.cap;
+  const uint32_t ep = *epoch_ptr(c, MCB_SITE_A2A_COMBINE, blockIdx.x);
+  // Leading barrier: every destination's expert outputs were written by kernels that
+  // finished before its block arrived here.
+  block_barrier_all(c, MCB_SITE_A2A_COMBINE, blockIdx.x, ep);
+
+  const int row_packs = a.hidden / 8;
+  const uint64_t row_bytes = (uint64_t)a.hidden * 2;
+  uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
+  DestList& L = s_list[warp];
+  for (int t = blockIdx.x * nwarps + warp; t < n; t += gridDim.x * nwarps) {
+    int m = 0;
+    for (int d0 = 0; d0 < W; d0 += 32) {
+      const int d = d0 + lane;
+      const int slot = d < W ? a.slot_map[(long long)t * W + d] : -1;
+      const uint32_t have = __ballot_sync(0xffffffffu, slot >= 0);
+      if (slot >= 0) {
+        const int pos = m + __popc(have & ((1u << lane) - 1u));
+        L.dst[pos] = d;
+        L.slot[pos] = slot;
+      }
+      m += __popc(have);
+    }
+    __syncwarp();
+    for (int p = lane; p < row_packs; p += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      int j = 0;
+      for (; j + 4 <= m; j += 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          v[u] = ld_v4_stream(c.heap_peer[L.dst[j + u]] + a.y_off +
+                              ((uint64_t)c.rank * a.cap + L.slot[j + u]) * row_bytes + p * 16);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          acc[0] += bf16_lo(v[u].x); acc[1] += bf16_hi(v[u].x);
+          acc[2] += bf16_lo(v[u].y); acc[3] += bf16_hi(v[u].y);
+          acc[4] += bf16_lo(v[u].z); acc[5] += bf16_hi(v[u].z);
+          acc[6] += bf16_lo(v[u].w); acc[7] += bf16_hi(v[u].w);
+        }
+      }
+      for (; j < m; ++j) {
+        const uint4 v = ld_v4_stream(c.heap_peer[L.dst[j]] + a.y_off +
+                                     ((uint64_t)c.rank * a.cap + L.slot[j]) * row_bytes + p * 16);
+        acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x);
+        acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+        acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z);
+        acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+      }
+      st_v4(out + (uint64_t)t * row_bytes + p * 16,
+            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7])));
+    }
+    __syncwarp();
+  }
+}
+
+}  // namespace mcb
+
+using namespace mcb;
+
+extern "C" {
+
+static int check_a2a_launch(int grid, int threads) {
+  if (grid < 1 || grid > MCB_MAX_BLOCKS || threads < 32 || threads > 512 || (threads & 31)) return 1;
+  return 0;
+}
+
+int mcb_launch_a2a_dispatch(const McbCtx* ctx, const McbA2ADispatchArgs* args, int grid, int threads,
+                            int pdl, cudaStream_t stream) {
+  if (check_a2a_launch(grid, threads)) return cudaErrorInvalidValue;
+  if (args->hidden % 8 || (args->fp8 && args->hidden % 128) || args->num_experts % ctx->world)
+    return cudaErrorInvalidValue;
+  return launch_kernel(a2a_dispatch_kernel<false>, dim3(grid), dim3(threads), 0, stream, pdl, false, *ctx,
+                       *args, (const McbCtx*)nullptr, (const McbA2ADispatchArgs*)nullptr);
+}
+
+int mcb_launch_a2a_combine(const McbCtx* ctx, const McbA2ACombineArgs* args, int grid, int threads, int pdl,
+                           cudaStream_t stream) {
+  if (check_a2a_launch(grid, threads)) return cudaErrorInvalidValue;
+  if (args->hidden % 8) return cudaErrorInvalidValue;
+  return launch_kernel(a2a_combine_kernel<false>, dim3(grid), dim3(threads), 0, stream, pdl, false, *ctx,
+                       *args, (const McbCtx*)nullptr, (const McbA2ACombineArgs*)nullptr);
+}
+
+// One decode step of the all-to-all dispatcher: num_layers x (dispatch, combine), issued
+// natively (role of DeepEPBencher.decode_step, bench_deepep.py:96-101).
+int mcb_a2a_decode_step(const McbCtx* ctx, const McbA2ADispatchArgs* d, const McbA2ACombineArgs* cmb,
+                        int num_layers, int grid, int threads, int pdl, cudaStream_t stream) {
+  int err = 0;
+  for (int l = 0; l < num_layers && err == 0; ++l) {
+    err = mcb_launch_a2a_dispatch(ctx, d, grid, threads, pdl, stream);
+    if (err == 0) err = mcb_launch_a2a_combine(ctx, cmb, grid, threads, pdl, stream);
+  }
+  return err;
+}
+
+int mcb_emu_a2a_dispatch(const McbCtx* d_ctx, const McbA2ADispatchArgs* d_args, int world, int grid,
+                         int threads, cudaStream_t stream) {
+  if (check_a2a_launch(grid, threads)) return cudaErrorInvalidValue;
+  McbCtx dummy{};
+  McbA2ADispatchArgs dargs{};
+  return launch_kernel(a2a_dispatch_kernel<true>, dim3(grid, world), dim3(threads), 0, stream, 0, true, dummy,
+                       dargs, d_ctx, d_args);
+}
+
+int mcb_emu_a2a_combine(const McbCtx* d_ctx, const McbA2ACombineArgs* d_args, int world, int grid,
+                        int threads, cudaStream_t stream) {
+  if (check_a2a_launch(grid, threads)) return cudaErrorInvalidValue;
+  McbCtx dummy{};
+  McbA2ACombineArgs dargs{};
+  return launch_kernel(a2a_combine_kernel<true>, dim3(grid, world), dim3(threads), 0, stream, 0, true, dummy,
+                       dargs, d_ctx, d_args);
+}
+
+}  // extern "C"

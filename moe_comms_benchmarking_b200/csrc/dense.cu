@@ -1,0 +1,386 @@
+// Dense expert-parallel transport for sm_100a: token-count metadata, variable all-gather
+// (dispatch) and variable reduce-scatter (combine) over NVSwitch.
+//
+// Same capabilities as the reference's Triton kernels
+//   nvls/metadata.py:46-139                          (count exchange -> [sum, prefix, max])
+//   nvls/torch_symm_triton/variable_collectives.py:40-150, 366-544   (AllGather-V, 1 and 3 tensors)
+//   nvls/torch_symm_triton/variable_collectives.py:153-258           (ReduceScatter-V)
+// with a different design:
+//   * every size that changes between steps (local token count, prefix offset, max) is read
+//     from device memory, so one captured CUDA graph serves any batch up to the capacity;
+//   * tensors are copied as flat byte ranges (rows are packed), 4 independent 16-byte
+//     accesses per thread in flight, with a block count that grows with the largest rank's
+//     token count and is the same on every rank;
+//   * the barrier is the one-way epoch barrier of mcb_barrier.cuh (no CAS round trip), and
+//     every kernel issues griddepcontrol so consecutive layers can overlap launch latency;
+//   * each kernel runs with either transport: NVSwitch multicast (multimem.*) or plain peer
+//     loads/stores (also the path used for world == 1 and for single-GPU emulation).
+//
+// Emulation (EMU = true): one cooperative launch with gridDim.y = world runs all ranks of a
+// collective on one GPU, each y-slice using its own context; used to test the multi-rank
+// protocol where only one GPU is available.
+#include <cooperative_groups.h>
+#include <cuda_runtime.h>
+
+#include "mcb_barrier.cuh"
+#include "mcb_launch.h"
+
+namespace mcb {
+
+__device__ __forceinline__ int ceil_div_i(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// ------------------------------------------------------------------------------------------
+// Metadata: publish this rank's count to every rank, barrier, reduce to [sum, prefix, max].
+// ------------------------------------------------------------------------------------------
+template <bool EMU>
+__global__ void __launch_bounds__(128) metadata_kernel(const __grid_constant__ McbCtx ctx_p,
+                                                       const __grid_constant__ McbMetaArgs args_p,
+                                                       const McbCtx* ectx, const McbMetaArgs* eargs) {
+  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
+  const McbMetaArgs& a = EMU ? eargs[blockIdx.y] : args_p;
+  __shared__ int s_counts[MCB_MAX_RANKS];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x;
+  const uint32_t ep = *epoch_ptr(c, MCB_SITE_META, 0);
+  const uint32_t par = ep & 1u;
+  int n = *a.n_local;
+  if (n < 0) n = 0;
+  if (n > a.cap) {
+    if (tid == 0) report_error(c, MCB_ERR_CAPACITY, MCB_SITE_META, 0, (uint32_t)n, (uint32_t)a.cap);
+    n = a.cap;
+  }
+  const uint64_t slot_off = a.counts_off + (uint64_t)(par * MCB_MAX_RANKS + c.rank) * sizeof(int32_t);
+  if (c.transport == MCB_TRANSPORT_MULTIMEM) {
+    if (tid == 0) mm_st_b32(c.heap_mc + slot_off, (uint32_t)n);
+  } else {
+    for (int p = tid; p < c.world; p += blockDim.x) st_relaxed_sys(c.heap_peer[p] + slot_off, (uint32_t)n);
+  }
+  // The signalling thread is the one that stored, so its release covers the store.
+  block_barrier_all(c, MCB_SITE_META, 0, ep);
+  const uint8_t* counts = c.heap_local + a.counts_off + (uint64_t)par * MCB_MAX_RANKS * sizeof(int32_t);
+  for (int p = tid; p < c.world; p += blockDim.x) s_counts[p] = (int)ld_relaxed_sys(counts + p * 4);
+  __syncthreads();
+  if (tid == 0) {
+    int sum = 0, prefix = 0, mx = 0;
+    for (int p = 0; p < c.world; ++p) {
+      const int v = s_counts[p];
+      sum += v;
+      if (p < c.rank) prefix += v;
+      mx = v > mx ? v : mx;
+    }
+    a.step_meta[0] = sum;
+    a.step_meta[1] = prefix;
+    a.step_meta[2] = mx;
+    a.step_meta[3] = (int)(ep + 1u);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Flat copy helpers.  VEC = bytes per access (16, 8 or 4).
+// ------------------------------------------------------------------------------------------
+template <int VEC> struct Pack;
+template <> struct Pack<16> {
+  using T = uint4;
+  static __device__ __forceinline__ T ld(const void* p) { return ld_v4_stream(p); }
+  static __device__ __forceinline__ void st(void* p, T v) { st_v4(p, v); }
+  static __device__ __forceinline__ void mm_st(void* p, T v) { mm_st_v4(p, v); }
+};
+template <> struct Pack<8> {
+  using T = uint2;
+  static __device__ __forceinline__ T ld(const void* p) { return ld_v2(p); }
+  static __device__ __forceinline__ void st(void* p, T v) { st_v2(p, v); }
+  static __device__ __forceinline__ void mm_st(void* p, T v) { mm_st_v2(p, v); }
+};
+template <> struct Pack<4> {
+  using T = uint32_t;
+  static __device__ __forceinline__ T ld(const void* p) { return ld_b32(p); }
+  static __device__ __forceinline__ void st(void* p, T v) { st_b32(p, v); }
+  static __device__ __forceinline__ void mm_st(void* p, T v) { mm_st_b32(p, v); }
+};
+
+constexpr int kUnroll = 4;
+
+// Broadcast `nbytes` from local `src` to heap offset `dst_off` on every rank.
+template <int VEC>
+__device__ __forceinline__ void broadcast_flat(const McbCtx& c, const uint8_t* src, uint64_t dst_off,
+                                               long long nbytes, long long start, long long stride) {
+  using P = Pack<VEC>;
+  const long long nvec = nbytes / VEC;
+  if (c.transport == MCB_TRANSPORT_MULTIMEM) {
+    uint8_t* dst = c.heap_mc + dst_off;
+    for (long long i = start; i < nvec; i += stride * kUnroll) {
+      typename P::T v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (i + u * stride < nvec) v[u] = P::ld(src + (i + u * stride) * VEC);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (i + u * stride < nvec) P::mm_st(dst + (i + u * stride) * VEC, v[u]);
+    }
+  } else {
+    for (long long i = start; i < nvec; i += stride * kUnroll) {
+      typename P::T v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (i + u * stride < nvec) v[u] = P::ld(src + (i + u * stride) * VEC);
+      // Start with the next rank so that all ranks do not hit the same peer at once.
+      for (int k = 0; k < c.world; ++k) {
+        int p = c.rank + 1 + k;
+        if (p >= c.world) p -= c.world;
+        uint8_t* dst = c.heap_peer[p] + dst_off;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+          if (i + u * stride < nvec) P::st(dst + (i + u * stride) * VEC, v[u]);
+      }
+    }
+  }
+}
+
+// Number of blocks that take part in a variable collective.  Depends only on values that
+// are identical on every rank (grid size, largest per-rank count, bytes per row), so block b
+// either runs on all ranks or on none.
+__device__ __forceinline__ int active_blocks(int grid, int ep_max, long long bytes_per_row, int threads) {
+  if (ep_max <= 0) return 0;
+  const long long vecs = ((long long)ep_max * bytes_per_row + 15) / 16;
+  int nb = ceil_div_i(vecs, threads);
+  if (nb < 1) nb = 1;
+  return nb < grid ? nb : grid;
+}
+
+template <bool EMU>
+__global__ void __launch_bounds__(512) agv_kernel(const __grid_constant__ McbCtx ctx_p,
+                                                   const __grid_constant__ McbAgvArgs args_p,
+                                                   const McbCtx* ectx, const McbAgvArgs* eargs) {
+  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
+  const McbAgvArgs& a = EMU ? eargs[blockIdx.y] : args_p;
+  pdl_wait();
+  const int bid = blockIdx.x;
+  int n = *a.n_local;
+  const int offset = a.step_meta[1];
+  const int ep_max = a.step_meta[2];
+  long long bytes_per_row = 0;
+#pragma unroll
+  for (int t = 0; t < MCB_MAX_TENSORS; ++t)
+    if (t < a.num_tensors) bytes_per_row += a.row_bytes[t];
+  const int nact = active_blocks((int)gridDim.x, ep_max, bytes_per_row, (int)blockDim.x);
+  pdl_launch_dependents();
+  if (bid >= nact) return;
+  const uint32_t ep = *epoch_ptr(c, a.site, bid);
+  if (n < 0) n = 0;
+  if (n > a.cap || offset < 0 || (long long)offset + n > (long long)a.cap * c.world) {
+    if (threadIdx.x == 0)
+      report_error(c, n > a.cap ? MCB_ERR_CAPACITY : MCB_ERR_BOUNDS, (uint32_t)a.site, (uint32_t)bid,
+                   (uint32_t)n, (uint32_t)offset);
+    n = 0;  // skip the copy, still meet the barrier
+  }
+  const long long start = (long long)bid * blockDim.x + threadIdx.x;
+  const long long stride = (long long)nact * blockDim.x;
+#pragma unroll
+  for (int t = 0; t < MCB_MAX_TENSORS; ++t) {
+    if (t >= a.num_tensors) break;
+    const uint32_t rb = a.row_bytes[t];
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.src[t]);
+    const uint64_t dst_off = a.dst_off[t] + (uint64_t)offset * rb;
+    const long long nbytes = (long long)n * rb;
+    if ((rb & 15u) == 0) broadcast_flat<16>(c, src, dst_off, nbytes, start, stride);
+    else if ((rb & 7u) == 0) broadcast_flat<8>(c, src, dst_off, nbytes, start, stride);
+    else broadcast_flat<4>(c, src, dst_off, nbytes, start, stride);
+  }
+  // Trailing barrier: when this kernel has finished on a rank, every peer's rows are there.
+  block_barrier_all(c, a.site, bid, ep);
+}
+
+// ------------------------------------------------------------------------------------------
+// Reduce-scatter-V
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void acc_bf16x8(float (&acc)[8], uint4 v) {
+  acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x);
+  acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+  acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z);
+  acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+}
+
+// Sum of one 16-byte pack over every rank's heap with plain peer loads.
+template <bool F32>
+__device__ __forceinline__ uint4 p2p_reduce_pack(const McbCtx& c, uint64_t off) {
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  int k = 0;
+  for (; k + 4 <= c.world; k += 4) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int p = c.rank + k + u;
+      if (p >= c.world) p -= c.world;
+      v[u] = ld_v4_stream(c.heap_peer[p] + off);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (F32) {
+        acc[0] += __uint_as_float(v[u].x); acc[1] += __uint_as_float(v[u].y);
+        acc[2] += __uint_as_float(v[u].z); acc[3] += __uint_as_float(v[u].w);
+      } else {
+        acc_bf16x8(acc, v[u]);
+      }
+    }
+  }
+  for (; k < c.world; ++k) {
+    int p = c.rank + k;
+    if (p >= c.world) p -= c.world;
+    const uint4 v = ld_v4_stream(c.heap_peer[p] + off);
+    if (F32) {
+      acc[0] += __uint_as_float(v.x); acc[1] += __uint_as_float(v.y);
+      acc[2] += __uint_as_float(v.z); acc[3] += __uint_as_float(v.w);
+    } else {
+      acc_bf16x8(acc, v);
+    }
+  }
+  if (F32)
+    return make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]),
+                      __float_as_uint(acc[3]));
+  return make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                    pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+}
+
+template <bool EMU>
+__global__ void __launch_bounds__(512) rsv_kernel(const __grid_constant__ McbCtx ctx_p,
+                                                   const __grid_constant__ McbRsvArgs args_p,
+                                                   const McbCtx* ectx, const McbRsvArgs* eargs) {
+  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
+  const McbRsvArgs& a = EMU ? eargs[blockIdx.y] : args_p;
+  pdl_wait();
+  const int bid = blockIdx.x;
+  int n = *a.n_local;
+  const int offset = a.step_meta[1];
+  const int ep_max = a.step_meta[2];
+  const int nact = active_blocks((int)gridDim.x, ep_max, a.row_bytes, (int)blockDim.x);
+  pdl_launch_dependents();
+  if (bid >= nact) return;
+  const uint32_t ep = *epoch_ptr(c, a.site, bid);
+  if (n < 0) n = 0;
+  if (n > a.cap || offset < 0 || (long long)offset + n > (long long)a.cap * c.world) {
+    if (threadIdx.x == 0)
+      report_error(c, n > a.cap ? MCB_ERR_CAPACITY : MCB_ERR_BOUNDS, (uint32_t)a.site, (uint32_t)bid,
+                   (uint32_t)n, (uint32_t)offset);
+    n = 0;
+  }
+  // Leading barrier: every rank's partial sums were written by kernels that finished before
+  // that rank's block arrived here.
+  block_barrier_all(c, a.site, bid, ep);
+
+  const long long nvec = (long long)n * a.row_bytes / 16;
+  const long long start = (long long)bid * blockDim.x + threadIdx.x;
+  const long long stride = (long long)nact * blockDim.x;
+  const uint64_t base = a.src_off + (uint64_t)offset * a.row_bytes;
+  uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
+  if (c.transport == MCB_TRANSPORT_MULTIMEM) {
+    const uint8_t* src = c.heap_mc + base;
+    for (long long i = start; i < nvec; i += stride * kUnroll) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (i + u * stride < nvec)
+          v[u] = a.dtype == 1 ? mm_ld_reduce_f32x4(src + (i + u * stride) * 16)
+                              : mm_ld_reduce_bf16x8(src + (i + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (i + u * stride < nvec) st_v4(out + (i + u * stride) * 16, v[u]);
+    }
+  } else {
+    for (long long i = start; i < nvec; i += stride) {
+      const uint4 v = a.dtype == 1 ? p2p_reduce_pack<true>(c, base + i * 16)
+                                   : p2p_reduce_pack<false>(c, base + i * 16);
+      st_v4(out + i * 16, v);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Self-test of the barrier: `rounds` barriers on MCB_SITE_TEST.  With a context whose world
+// counts a rank that never signals, the bounded wait runs out and the status is set.
+// ------------------------------------------------------------------------------------------
+template <bool EMU>
+__global__ void barrier_test_kernel(const __grid_constant__ McbCtx ctx_p, const McbCtx* ectx, int rounds) {
+  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
+  for (int r = 0; r < rounds; ++r) {
+    const uint32_t ep = *epoch_ptr(c, MCB_SITE_TEST, blockIdx.x);
+    block_barrier_all(c, MCB_SITE_TEST, blockIdx.x, ep);
+  }
+}
+
+}  // namespace mcb
+
+// ------------------------------------------------------------------------------------------
+// Launchers
+// ------------------------------------------------------------------------------------------
+using namespace mcb;
+
+extern "C" {
+
+int mcb_launch_metadata(const McbCtx* ctx, const McbMetaArgs* args, int pdl, cudaStream_t stream) {
+  return launch_kernel(metadata_kernel<false>, dim3(1), dim3(128), 0, stream, pdl, false, *ctx, *args,
+                       (const McbCtx*)nullptr, (const McbMetaArgs*)nullptr);
+}
+
+int mcb_launch_agv(const McbCtx* ctx, const McbAgvArgs* args, int grid, int threads, int pdl,
+                   cudaStream_t stream) {
+  if (grid < 1 || grid > MCB_MAX_BLOCKS || threads < 32 || threads > 512) return cudaErrorInvalidValue;
+  return launch_kernel(agv_kernel<false>, dim3(grid), dim3(threads), 0, stream, pdl, false, *ctx, *args,
+                       (const McbCtx*)nullptr, (const McbAgvArgs*)nullptr);
+}
+
+int mcb_launch_rsv(const McbCtx* ctx, const McbRsvArgs* args, int grid, int threads, int pdl,
+                   cudaStream_t stream) {
+  if (grid < 1 || grid > MCB_MAX_BLOCKS || threads < 32 || threads > 512) return cudaErrorInvalidValue;
+  return launch_kernel(rsv_kernel<false>, dim3(grid), dim3(threads), 0, stream, pdl, false, *ctx, *args,
+                       (const McbCtx*)nullptr, (const McbRsvArgs*)nullptr);
+}
+
+// One decode step of the dense dispatcher, issued natively: metadata once, then
+// num_layers x (all-gather-V, reduce-scatter-V).  Mirrors NVLSBencher.decode_step
+// (bench_nvls.py:114-121) without a Python loop.
+int mcb_dense_decode_step(const McbCtx* ctx, const McbMetaArgs* meta, const McbAgvArgs* agv,
+                          const McbRsvArgs* rsv, int num_layers, int grid, int threads, int pdl,
+                          cudaStream_t stream) {
+  int err = mcb_launch_metadata(ctx, meta, pdl, stream);
+  for (int l = 0; l < num_layers && err == 0; ++l) {
+    err = mcb_launch_agv(ctx, agv, grid, threads, pdl, stream);
+    if (err == 0) err = mcb_launch_rsv(ctx, rsv, grid, threads, pdl, stream);
+  }
+  return err;
+}
+
+int mcb_launch_barrier_test(const McbCtx* ctx, int grid, int rounds, cudaStream_t stream) {
+  if (grid < 1 || grid > MCB_MAX_BLOCKS) return cudaErrorInvalidValue;
+  return launch_kernel(barrier_test_kernel<false>, dim3(grid), dim3(128), 0, stream, 0, false, *ctx,
+                       (const McbCtx*)nullptr, rounds);
+}
+
+// ---- single-GPU emulation of `world` ranks (contexts and arguments live in device memory) ----
+int mcb_emu_metadata(const McbCtx* d_ctx, const McbMetaArgs* d_args, int world, cudaStream_t stream) {
+  McbCtx dummy{};
+  McbMetaArgs dargs{};
+  return launch_kernel(metadata_kernel<true>, dim3(1, world), dim3(128), 0, stream, 0, true, dummy, dargs,
+                       d_ctx, d_args);
+}
+int mcb_emu_agv(const McbCtx* d_ctx, const McbAgvArgs* d_args, int world, int grid, int threads,
+                cudaStream_t stream) {
+  McbCtx dummy{};
+  McbAgvArgs dargs{};
+  return launch_kernel(agv_kernel<true>, dim3(grid, world), dim3(threads), 0, stream, 0, true, dummy, dargs,
+                       d_ctx, d_args);
+}
+int mcb_emu_rsv(const McbCtx* d_ctx, const McbRsvArgs* d_args, int world, int grid, int threads,
+                cudaStream_t stream) {
+  McbCtx dummy{};
+  McbRsvArgs dargs{};
+  return launch_kernel(rsv_kernel<true>, dim3(grid, world), dim3(threads), 0, stream, 0, true, dummy, dargs,
+                       d_ctx, d_args);
+}
+int mcb_emu_barrier_test(const McbCtx* d_ctx, int world, int grid, int rounds, cudaStream_t stream) {
+  McbCtx dummy{};
+  return launch_kernel(barrier_test_kernel<true>, dim3(grid, world), dim3(128), 0, stream, 0, true, dummy,
+                       d_ctx, rounds);
+}
+
+}  // extern "C"

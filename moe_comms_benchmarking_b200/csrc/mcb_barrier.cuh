@@ -1,0 +1,84 @@
+// Cross-GPU barrier with bounded waits and an error status word.
+//
+// Role of the reference's signal-pad barrier (nvls/torch_symm_triton/barrier.py:20-115),
+// redesigned for latency and for shared GPUs:
+//   * arrival is a one-way fire-and-forget add (multimem.red through the switch, or one
+//     red.release.sys per peer) instead of a CAS that needs the old value back;
+//   * slots are never reset: slot value after its k-th use is k * world, and each block
+//     keeps its own k ("epoch") in local memory, so a CUDA graph can be replayed without
+//     any host-side counter;
+//   * every wait has a time budget; when it runs out the kernel records
+//     {code, site, block, seen, wanted, rank} in the status words and carries on to its
+//     exit, so the context stays usable and the host raises the error.
+// The barrier is block-matched: block b of rank r meets block b of every other rank.
+#pragma once
+#include "mcb_ctx.h"
+#include "mcb_ptx.cuh"
+
+namespace mcb {
+
+__device__ __forceinline__ void report_error(const McbCtx& c, uint32_t code, uint32_t site,
+                                             uint32_t block, uint32_t seen, uint32_t wanted) {
+  if (atomicCAS(c.status, 0u, code) == 0u) {
+    c.status[1] = site;
+    c.status[2] = block;
+    c.status[3] = seen;
+    c.status[4] = wanted;
+    c.status[5] = (uint32_t)c.rank;
+  }
+}
+
+__device__ __forceinline__ uint32_t* flag_ptr(uint8_t* heap, const McbCtx& c, int site, int slot) {
+  return reinterpret_cast<uint32_t*>(heap + c.flags_off) + site * MCB_MAX_BLOCKS + slot;
+}
+__device__ __forceinline__ uint32_t* epoch_ptr(const McbCtx& c, int site, int slot) {
+  return c.epochs + site * MCB_MAX_BLOCKS + slot;
+}
+
+// Called by every thread of the block after a __syncthreads() that follows the block's
+// data writes.  Adds 1 to flag[site][slot] on every rank (self included).
+__device__ __forceinline__ void signal_all(const McbCtx& c, int site, int slot) {
+  if (c.transport == MCB_TRANSPORT_MULTIMEM) {
+    if (threadIdx.x == 0) mm_red_add_release(flag_ptr(c.heap_mc, c, site, slot), 1u);
+  } else {
+    for (int p = threadIdx.x; p < c.world; p += blockDim.x)
+      red_add_release_sys(flag_ptr(c.heap_peer[p], c, site, slot), 1u);
+  }
+}
+
+// Called by ONE thread.  Spins until flag[site][slot] reached `target` (wrap-safe) or the
+// time budget ran out.  Returns false on timeout after recording the error.
+__device__ __forceinline__ bool wait_flag(const McbCtx& c, int site, int slot, uint32_t target) {
+  const uint32_t* f = flag_ptr(c.heap_local, c, site, slot);
+  uint32_t v = ld_acquire_sys(f);
+  if ((int32_t)(v - target) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      v = ld_acquire_sys(f);
+      if ((int32_t)(v - target) >= 0) return true;
+    }
+    // Once any wait on this rank has failed, later waits give up at once so that the rest of
+    // a captured multi-layer graph drains quickly instead of timing out kernel by kernel.
+    const bool poisoned = *reinterpret_cast<volatile uint32_t*>(c.status) != 0u;
+    if (poisoned || globaltimer_ns() - t0 > c.timeout_ns) {
+      report_error(c, MCB_ERR_TIMEOUT, (uint32_t)site, (uint32_t)slot, v, target);
+      return false;
+    }
+  }
+}
+
+// Whole-block barrier with every other rank's block `slot`.  `ep` is the block's epoch
+// read earlier from epoch_ptr(); the epoch is advanced here.  Ends with __syncthreads().
+__device__ __forceinline__ void block_barrier_all(const McbCtx& c, int site, int slot, uint32_t ep) {
+  __syncthreads();
+  signal_all(c, site, slot);
+  if (threadIdx.x == 0) {
+    wait_flag(c, site, slot, (ep + 1u) * (uint32_t)c.world);
+    *epoch_ptr(c, site, slot) = ep + 1u;
+  }
+  __syncthreads();
+}
+
+}  // namespace mcb

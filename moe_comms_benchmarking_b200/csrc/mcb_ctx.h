@@ -1,0 +1,145 @@
+// Host/device shared plain-C structures of the MoE comms kernels.
+//
+// Every struct here is mirrored field by field with ctypes in ops/_ext.py; the
+// library exports mcb_sizeof_* so the Python side can assert the layouts agree.
+//
+// Memory model: each rank owns one *symmetric heap* (same size, same internal
+// offsets on every rank).  A buffer is named by its byte offset into the heap;
+// the same offset is valid against the local base, any peer's mapped base, and
+// (when an NVSwitch multicast object is bound) the multicast base.
+#pragma once
+#include <stdint.h>
+
+#define MCB_MAX_RANKS 72      // one NVL72 NVLink domain
+#define MCB_MAX_BLOCKS 512    // flag slots per barrier site
+#define MCB_NUM_SITES 16      // independent barrier sites
+#define MCB_STATUS_WORDS 8
+
+// Transports for the cross-GPU part of a kernel.
+#define MCB_TRANSPORT_P2P 0        // plain peer ld/st/red through NVLink mappings
+#define MCB_TRANSPORT_MULTIMEM 1   // NVSwitch multicast: multimem.st / multimem.ld_reduce / multimem.red
+
+// Barrier sites (one flag row each) so that different kernel families never share slots.
+#define MCB_SITE_META 0
+#define MCB_SITE_AGV 1
+#define MCB_SITE_RSV 2
+#define MCB_SITE_A2A_DISPATCH 3
+#define MCB_SITE_A2A_COMBINE 4
+#define MCB_SITE_UNIFORM_AG 5
+#define MCB_SITE_UNIFORM_RS 6
+#define MCB_SITE_NORM_IN 7
+#define MCB_SITE_NORM_OUT 8
+#define MCB_SITE_FUSED_FC1 9
+#define MCB_SITE_FUSED_FC2 10
+#define MCB_SITE_LAYER 11
+#define MCB_SITE_TEST 15
+
+// Status codes written to status[0] (first error wins; 0 = healthy).
+#define MCB_OK 0
+#define MCB_ERR_TIMEOUT 1        // a bounded cross-GPU wait ran out
+#define MCB_ERR_CAPACITY 2       // a token count exceeded the buffer capacity
+#define MCB_ERR_BOUNDS 3         // an offset fell outside its buffer
+#define MCB_ERR_ROUTING 4        // an expert id outside [0, num_experts)
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Per-rank communication context, passed by value to every kernel.
+typedef struct {
+  int32_t rank;
+  int32_t world;
+  int32_t transport;           // MCB_TRANSPORT_*
+  int32_t reserved0;
+  uint64_t timeout_ns;         // budget of each bounded wait
+  uint8_t* heap_local;         // this rank's heap
+  uint8_t* heap_mc;            // multicast alias of the heap (NULL without NVLS)
+  uint64_t flags_off;          // heap offset of uint32 flags[MCB_NUM_SITES][MCB_MAX_BLOCKS]
+  uint32_t* epochs;            // local (not symmetric) uint32 epochs[MCB_NUM_SITES][MCB_MAX_BLOCKS]
+  uint32_t* status;            // local uint32 status[MCB_STATUS_WORDS]
+  uint8_t* heap_peer[MCB_MAX_RANKS];  // every rank's heap as mapped here (heap_peer[rank] == heap_local)
+} McbCtx;
+
+// Token-count exchange: counts -> step_meta = [valid(sum), offset(prefix), max, 0].
+typedef struct {
+  const int32_t* n_local;      // device scalar: this rank's token count
+  uint64_t counts_off;         // heap offset of int32 counts[2][MCB_MAX_RANKS] (parity double buffer)
+  int32_t* step_meta;          // local int32[4]
+  int32_t cap;                 // per-rank capacity (n_local > cap raises MCB_ERR_CAPACITY)
+  int32_t reserved0;
+} McbMetaArgs;
+
+#define MCB_MAX_TENSORS 4
+
+// Variable all-gather of up to MCB_MAX_TENSORS row-major tensors into packed
+// [sum(n), row_bytes] heap buffers at row offset step_meta[1].
+typedef struct {
+  const void* src[MCB_MAX_TENSORS];
+  uint64_t dst_off[MCB_MAX_TENSORS];
+  uint32_t row_bytes[MCB_MAX_TENSORS];
+  int32_t num_tensors;
+  int32_t cap;                 // per-rank row capacity
+  int32_t site;
+  int32_t reserved0;
+  const int32_t* n_local;
+  const int32_t* step_meta;
+} McbAgvArgs;
+
+// Variable reduce-scatter: out[t,:] = sum over ranks of heap[src_off][(offset+t),:].
+typedef struct {
+  void* out;
+  uint64_t src_off;
+  uint32_t row_bytes;
+  int32_t dtype;               // 0 = bf16 operands with fp32 accumulation, 1 = fp32
+  int32_t cap;
+  int32_t site;
+  const int32_t* n_local;
+  const int32_t* step_meta;
+} McbRsvArgs;
+
+// All-to-all-V dispatch (one copy of a token per distinct destination rank).
+typedef struct {
+  const void* x;               // [n, hidden] bf16
+  const int64_t* topk_idx;     // [n, topk]
+  const float* topk_w;         // [n, topk] (may be NULL)
+  uint64_t recv_x_off;         // heap: [world][cap][hidden] bf16, or e4m3 when fp8 != 0
+  uint64_t recv_scale_off;     // heap: [world][cap][hidden/128] fp32 (fp8 only)
+  uint64_t recv_idx_off;       // heap: [world][cap][topk] int64
+  uint64_t recv_w_off;         // heap: [world][cap][topk] fp32
+  uint64_t recv_src_off;       // heap: [world][cap] int32 source token index
+  uint64_t recv_count_off;     // heap: [MCB_MAX_RANKS] int32 rows received from each source
+  int32_t* slot_map;           // local [cap][world] int32: slot on each destination, -1 = not sent
+  int32_t* send_count;         // local [MCB_MAX_RANKS + 1] int32 scratch (last word = blocks done)
+  const int32_t* n_local;
+  int32_t hidden;
+  int32_t topk;
+  int32_t num_experts;
+  int32_t cap;
+  int32_t fp8;
+  int32_t reserved0;
+} McbA2ADispatchArgs;
+
+// All-to-all-V combine: out[t,:] = sum over destination ranks d of y_d[rank][slot_map[t][d],:].
+typedef struct {
+  void* out;                   // [n, hidden] bf16
+  uint64_t y_off;              // heap: [world][cap][hidden] bf16 expert outputs in receive layout
+  const int32_t* slot_map;
+  const int32_t* n_local;
+  int32_t hidden;
+  int32_t cap;
+} McbA2ACombineArgs;
+
+// Reduce-scatter + residual add + RMSNorm + all-gather, in place in a heap buffer.
+typedef struct {
+  uint64_t buf_off;            // heap: [tokens][hidden] bf16 partial sums in, normalised rows out
+  void* residual;              // local [tokens/world][hidden] bf16, updated in place
+  const void* weight;          // [hidden] bf16
+  float eps;
+  int32_t hidden;
+  int32_t tokens;              // total rows (multiple of world)
+  int32_t reserved0;
+} McbNormArgs;
+
+#ifdef __cplusplus
+}
+#endif

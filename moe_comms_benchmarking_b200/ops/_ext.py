@@ -1,0 +1,146 @@
+"""ctypes binding of ``lib/libmcb.so`` (the hand-written sm_100a kernels).
+
+The C structures of ``csrc/mcb_ctx.h`` are mirrored here field by field; ``load()`` checks
+every ``sizeof`` against the library so a drifted layout fails at import time instead of
+corrupting a launch.  There is no fallback: on a machine with a GPU a missing library is an
+error (``require()``), so a GPU test can never pass on a silent PyTorch path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+MAX_RANKS = 72
+MAX_BLOCKS = 512
+NUM_SITES = 16
+STATUS_WORDS = 8
+MAX_TENSORS = 4
+
+TRANSPORT_P2P = 0
+TRANSPORT_MULTIMEM = 1
+
+SITE_META, SITE_AGV, SITE_RSV = 0, 1, 2
+SITE_A2A_DISPATCH, SITE_A2A_COMBINE = 3, 4
+SITE_UNIFORM_AG, SITE_UNIFORM_RS = 5, 6
+SITE_NORM_IN, SITE_NORM_OUT = 7, 8
+SITE_FUSED_FC1, SITE_FUSED_FC2, SITE_LAYER, SITE_TEST = 9, 10, 11, 15
+
+ERR_NAMES = {0: "ok", 1: "timeout", 2: "capacity", 3: "bounds", 4: "routing"}
+
+_vp, _u64, _i32, _u32, _f32 = C.c_void_p, C.c_uint64, C.c_int32, C.c_uint32, C.c_float
+
+
+class McbCtx(C.Structure):
+    _fields_ = [
+        ("rank", _i32), ("world", _i32), ("transport", _i32), ("reserved0", _i32),
+        ("timeout_ns", _u64),
+        ("heap_local", _vp), ("heap_mc", _vp), ("flags_off", _u64),
+        ("epochs", _vp), ("status", _vp),
+        ("heap_peer", _vp * MAX_RANKS),
+    ]
+
+
+class McbMetaArgs(C.Structure):
+    _fields_ = [("n_local", _vp), ("counts_off", _u64), ("step_meta", _vp), ("cap", _i32),
+                ("reserved0", _i32)]
+
+
+class McbAgvArgs(C.Structure):
+    _fields_ = [
+        ("src", _vp * MAX_TENSORS), ("dst_off", _u64 * MAX_TENSORS), ("row_bytes", _u32 * MAX_TENSORS),
+        ("num_tensors", _i32), ("cap", _i32), ("site", _i32), ("reserved0", _i32),
+        ("n_local", _vp), ("step_meta", _vp),
+    ]
+
+
+class McbRsvArgs(C.Structure):
+    _fields_ = [
+        ("out", _vp), ("src_off", _u64), ("row_bytes", _u32), ("dtype", _i32), ("cap", _i32),
+        ("site", _i32), ("n_local", _vp), ("step_meta", _vp),
+    ]
+
+
+class McbA2ADispatchArgs(C.Structure):
+    _fields_ = [
+        ("x", _vp), ("topk_idx", _vp), ("topk_w", _vp),
+        ("recv_x_off", _u64), ("recv_scale_off", _u64), ("recv_idx_off", _u64), ("recv_w_off", _u64),
+        ("recv_src_off", _u64), ("recv_count_off", _u64),
+        ("slot_map", _vp), ("send_count", _vp), ("n_local", _vp),
+        ("hidden", _i32), ("topk", _i32), ("num_experts", _i32), ("cap", _i32), ("fp8", _i32),
+        ("reserved0", _i32),
+    ]
+
+
+class McbA2ACombineArgs(C.Structure):
+    _fields_ = [("out", _vp), ("y_off", _u64), ("slot_map", _vp), ("n_local", _vp), ("hidden", _i32),
+                ("cap", _i32)]
+
+
+class McbNormArgs(C.Structure):
+    _fields_ = [("buf_off", _u64), ("residual", _vp), ("weight", _vp), ("eps", _f32), ("hidden", _i32),
+                ("tokens", _i32), ("reserved0", _i32)]
+
+
+_STRUCTS = {
+    "ctx": McbCtx, "meta_args": McbMetaArgs, "agv_args": McbAgvArgs, "rsv_args": McbRsvArgs,
+    "a2a_dispatch_args": McbA2ADispatchArgs, "a2a_combine_args": McbA2ACombineArgs, "norm_args": McbNormArgs,
+}
+
+LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libmcb.so"
+_lib = None
+
+
+class ExtensionMissing(RuntimeError):
+    pass
+
+
+class CudaLaunchError(RuntimeError):
+    pass
+
+
+def available() -> bool:
+    return LIB_PATH.exists()
+
+
+def load():
+    """Load the library once and verify the struct layouts."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ExtensionMissing(
+            f"{LIB_PATH} is missing: build it with `python -m moe_comms_benchmarking_b200.build`")
+    lib = C.CDLL(os.fspath(LIB_PATH))
+    for name, struct in _STRUCTS.items():
+        fn = getattr(lib, f"mcb_sizeof_{name}")
+        fn.restype = C.c_int
+        got, want = fn(), C.sizeof(struct)
+        if got != want:
+            raise ExtensionMissing(f"layout drift: sizeof({name}) is {got} in libmcb.so, {want} in ctypes")
+    lib.mcb_error_string.restype = C.c_char_p
+    lib.mcb_error_string.argtypes = [C.c_int]
+    _lib = lib
+    return lib
+
+
+def require():
+    """Like ``load`` but phrased for hot paths: never fall back, fail loudly."""
+    return load()
+
+
+def check(err: int, what: str) -> None:
+    if err != 0:
+        msg = load().mcb_error_string(err).decode()
+        raise CudaLaunchError(f"{what}: CUDA error {err} ({msg})")
+
+
+def ptr(t) -> int:
+    """Raw device address of a tensor (0 for None)."""
+    return 0 if t is None else t.data_ptr()
+
+
+def stream_handle(stream=None) -> C.c_void_p:
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)

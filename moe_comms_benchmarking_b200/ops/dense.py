@@ -1,0 +1,185 @@
+"""Dense expert-parallel collectives on the symmetric heap: token-count metadata,
+variable all-gather (dispatch) and variable reduce-scatter (combine), plus the
+uniform-count all-gather / reduce-scatter built on the same kernels.
+
+API surface of the reference's op layer (nvls/torch_symm_triton/__init__.py:3-10,
+nvls/metadata.py:111-139): ``fused_metadata_update``, ``multimem_all_gather_v``,
+``multimem_all_gatherv_3tensor``, ``multimem_reduce_scatter_v``, ``multimem_all_gather``,
+``multimem_all_gather_fused`` and ``multimem_reduce_scatter`` map to ``MetadataPlan``,
+``AllGatherVPlan`` (1 to 4 tensors), ``ReduceScatterVPlan`` and the ``uniform_*`` helpers.
+
+A *plan* owns the C argument block of one kernel; building it validates shapes, alignment
+and capacities on the host (the substitute for a device-side sanitizer), launching it is one
+ctypes call.  All per-step sizes are read by the kernels from device memory, so a plan (and
+a CUDA graph that contains it) stays valid while the batch changes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _ext
+from ..parallel.symm_heap import HeapTensor, SymmetricHeap
+
+DEFAULT_GRID = 148      # one block per B200 SM
+DEFAULT_THREADS = 512
+
+
+def _check_heap_tensor(heap: SymmetricHeap, ht: HeapTensor, what: str):
+    if ht.offset < 0 or ht.offset + ht.nbytes > heap.nbytes:
+        raise ValueError(f"{what}: heap range [{ht.offset}, {ht.offset + ht.nbytes}) outside the heap")
+    if ht.offset % 16:
+        raise ValueError(f"{what}: heap offset {ht.offset} is not 16-byte aligned")
+
+
+def _row_bytes(t: torch.Tensor) -> int:
+    if t.dim() != 2:
+        raise ValueError("expected a 2-D [rows, cols] tensor")
+    if not t.is_contiguous():
+        raise ValueError("expected a contiguous tensor")
+    return t.shape[1] * t.element_size()
+
+
+def _check_grid(grid: int, threads: int):
+    if not (1 <= grid <= _ext.MAX_BLOCKS):
+        raise ValueError(f"grid {grid} outside [1, {_ext.MAX_BLOCKS}]")
+    if not (32 <= threads <= 512) or threads % 32:
+        raise ValueError(f"threads {threads} must be a multiple of 32 in [32, 512]")
+
+
+class MetadataPlan:
+    """counts -> ``step_meta = [valid, offset, max, epoch]`` (int32, local device tensor)."""
+
+    def __init__(self, heap: SymmetricHeap, n_local: torch.Tensor, step_meta: torch.Tensor, cap: int):
+        if n_local.dtype != torch.int32 or n_local.numel() != 1:
+            raise ValueError("n_local must be an int32 scalar tensor on the device")
+        if step_meta.dtype != torch.int32 or step_meta.numel() < 4:
+            raise ValueError("step_meta must be int32[4]")
+        self.heap, self.n_local, self.step_meta = heap, n_local, step_meta
+        a = _ext.McbMetaArgs()
+        a.n_local = n_local.data_ptr()
+        a.counts_off = heap.counts_off
+        a.step_meta = step_meta.data_ptr()
+        a.cap = int(cap)
+        self.args = a
+
+    def launch(self, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        _ext.check(lib.mcb_launch_metadata(C.byref(self.heap.ctx()), C.byref(self.args), int(pdl),
+                                           _ext.stream_handle(stream)), "metadata")
+
+
+class AllGatherVPlan:
+    """Gather ``srcs[i][:n]`` of every rank into packed ``dsts[i]`` at row offset
+    ``step_meta[1]``.  1 to 4 tensors per launch; rows must be multiples of 4 bytes
+    (16-byte rows use 128-bit accesses, 8-byte rows 64-bit)."""
+
+    def __init__(self, heap: SymmetricHeap, dsts, srcs, n_local, step_meta, cap: int,
+                 site: int = _ext.SITE_AGV, grid: int = DEFAULT_GRID, threads: int = DEFAULT_THREADS):
+        if not (1 <= len(srcs) <= _ext.MAX_TENSORS) or len(srcs) != len(dsts):
+            raise ValueError(f"need 1..{_ext.MAX_TENSORS} (dst, src) pairs")
+        _check_grid(grid, threads)
+        self.heap, self.grid, self.threads = heap, grid, threads
+        self._keep = (list(dsts), list(srcs), n_local, step_meta)
+        a = _ext.McbAgvArgs()
+        gcap = cap * heap.world
+        for i, (d, s) in enumerate(zip(dsts, srcs)):
+            rb = _row_bytes(s)
+            _check_heap_tensor(heap, d, f"all_gather_v dst[{i}]")
+            if rb % 4:
+                raise ValueError(f"row of tensor {i} is {rb} bytes; must be a multiple of 4")
+            if d.tensor.dtype != s.dtype or d.tensor.shape[1:] != s.shape[1:]:
+                raise ValueError(f"tensor {i}: dst/src dtype or row shape differ")
+            if s.shape[0] < cap:
+                raise ValueError(f"tensor {i}: source holds {s.shape[0]} rows, capacity is {cap}")
+            if d.nbytes < gcap * rb:
+                raise ValueError(f"tensor {i}: gathered buffer too small for {gcap} rows of {rb} bytes")
+            if s.data_ptr() % 16:
+                raise ValueError(f"tensor {i}: source is not 16-byte aligned")
+            a.src[i] = s.data_ptr()
+            a.dst_off[i] = d.offset
+            a.row_bytes[i] = rb
+        a.num_tensors, a.cap, a.site = len(srcs), int(cap), int(site)
+        a.n_local, a.step_meta = n_local.data_ptr(), step_meta.data_ptr()
+        self.args = a
+
+    def launch(self, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        _ext.check(lib.mcb_launch_agv(C.byref(self.heap.ctx()), C.byref(self.args), self.grid, self.threads,
+                                      int(pdl), _ext.stream_handle(stream)), "all_gather_v")
+
+
+class ReduceScatterVPlan:
+    """``out[t] = sum over ranks of src[offset + t]`` for this rank's rows; bf16 operands are
+    accumulated in fp32 (in the switch with multimem), fp32 operands in fp32."""
+
+    def __init__(self, heap: SymmetricHeap, out: torch.Tensor, src: HeapTensor, n_local, step_meta, cap: int,
+                 site: int = _ext.SITE_RSV, grid: int = DEFAULT_GRID, threads: int = DEFAULT_THREADS):
+        _check_grid(grid, threads)
+        rb = _row_bytes(out)
+        _check_heap_tensor(heap, src, "reduce_scatter_v src")
+        if out.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("reduce_scatter_v supports bf16 and fp32")
+        if out.dtype != src.tensor.dtype:
+            raise ValueError("reduce_scatter_v: output and input dtypes differ")
+        if rb % 16:
+            raise ValueError(f"reduce_scatter_v rows must be multiples of 16 bytes (got {rb})")
+        if out.shape[0] < cap or src.nbytes < cap * heap.world * rb:
+            raise ValueError("reduce_scatter_v: buffers smaller than the capacity")
+        self.heap, self.grid, self.threads = heap, grid, threads
+        self._keep = (out, src, n_local, step_meta)
+        a = _ext.McbRsvArgs()
+        a.out, a.src_off, a.row_bytes = out.data_ptr(), src.offset, rb
+        a.dtype = 1 if out.dtype == torch.float32 else 0
+        a.cap, a.site = int(cap), int(site)
+        a.n_local, a.step_meta = n_local.data_ptr(), step_meta.data_ptr()
+        self.args = a
+
+    def launch(self, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        _ext.check(lib.mcb_launch_rsv(C.byref(self.heap.ctx()), C.byref(self.args), self.grid, self.threads,
+                                      int(pdl), _ext.stream_handle(stream)), "reduce_scatter_v")
+
+
+def dense_decode_step(heap, meta: MetadataPlan, agv: AllGatherVPlan, rsv: ReduceScatterVPlan,
+                      num_layers: int, pdl: bool = False, stream=None):
+    """metadata once, then ``num_layers`` x (all-gather-V, reduce-scatter-V), issued by one
+    native call (bench_nvls.py:114-121 does this loop in Python)."""
+    lib = _ext.require()
+    _ext.check(lib.mcb_dense_decode_step(C.byref(heap.ctx()), C.byref(meta.args), C.byref(agv.args),
+                                         C.byref(rsv.args), int(num_layers), agv.grid, agv.threads, int(pdl),
+                                         _ext.stream_handle(stream)), "dense_decode_step")
+
+
+# ---- uniform-count collectives (tensor-parallel style) ------------------------------------------
+def _uniform_meta(heap: SymmetricHeap, rows_per_rank: int):
+    dev = heap.device
+    n_local = torch.tensor([rows_per_rank], dtype=torch.int32, device=dev)
+    step_meta = torch.tensor([rows_per_rank * heap.world, rows_per_rank * heap.rank, rows_per_rank, 0],
+                             dtype=torch.int32, device=dev)
+    return n_local, step_meta
+
+
+class UniformAllGatherPlan(AllGatherVPlan):
+    """Equal-count all-gather of 1 to 4 tensors with one barrier (collectives.py:230-320 of the
+    reference): rank r's rows land at ``[r * rows, (r + 1) * rows)``."""
+
+    def __init__(self, heap, dsts, srcs, grid: int = DEFAULT_GRID, threads: int = DEFAULT_THREADS):
+        rows = srcs[0].shape[0]
+        if any(s.shape[0] != rows for s in srcs):
+            raise ValueError("uniform all-gather: all sources need the same number of rows")
+        n_local, step_meta = _uniform_meta(heap, rows)
+        super().__init__(heap, dsts, srcs, n_local, step_meta, cap=rows, site=_ext.SITE_UNIFORM_AG,
+                         grid=grid, threads=threads)
+
+
+class UniformReduceScatterPlan(ReduceScatterVPlan):
+    """Equal-count reduce-scatter (collectives.py:323-368): ``out`` = this rank's row block of
+    the cross-rank sum."""
+
+    def __init__(self, heap, out, src, grid: int = DEFAULT_GRID, threads: int = DEFAULT_THREADS):
+        rows = out.shape[0]
+        n_local, step_meta = _uniform_meta(heap, rows)
+        super().__init__(heap, out, src, n_local, step_meta, cap=rows, site=_ext.SITE_UNIFORM_RS,
+                         grid=grid, threads=threads)

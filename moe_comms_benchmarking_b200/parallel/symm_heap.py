@@ -1,0 +1,255 @@
+"""Symmetric heap: one allocation per rank, mapped into every peer and (with NVLS) bound
+to an NVSwitch multicast object, plus a bump sub-allocator and a keyed registry.
+
+Role of the reference's ``SymmetricMemoryManager`` / ``SymmetricMemoryBuffer``
+(nvls/symmetric_memory.py:34-184).  Differences by design:
+
+* ONE heap holds every buffer (the reference makes one symmetric allocation per tensor
+  and always hands out offset 0, symmetric_memory.py:73-77), so a kernel needs one local
+  base, one multicast base and one peer table, and names buffers by heap offset;
+* the barrier flags live inside the heap with an explicit size
+  (sites x blocks x 4 bytes), not in a library-sized signal pad;
+* a heap also exists for a world of one and for CPU ranks (plain local memory), so the
+  same dispatcher code runs at EP=1, in single-GPU emulation and under gloo.
+
+PyTorch's CUDA symmetric memory is used as the host-side allocator for world > 1: it
+creates the VMM allocation, exchanges handles and binds the multicast object; the kernels
+only ever see raw addresses.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _ext
+
+ALIGN = 256
+FLAGS_BYTES = _ext.NUM_SITES * _ext.MAX_BLOCKS * 4
+COUNTS_BYTES = 2 * _ext.MAX_RANKS * 4
+RESERVED_BYTES = ((FLAGS_BYTES + COUNTS_BYTES + ALIGN - 1) // ALIGN) * ALIGN
+
+
+class DeviceStatusError(RuntimeError):
+    """A kernel recorded an error in the status words (timeout, capacity, bounds, routing)."""
+
+    def __init__(self, words):
+        self.words = list(words)
+        code, site, block, seen, wanted, rank = self.words[:6]
+        name = _ext.ERR_NAMES.get(code, f"code{code}")
+        super().__init__(f"device status: {name} at site {site} block {block} on rank {rank} "
+                         f"(seen={seen}, wanted={wanted})")
+        self.code = code
+
+
+def _align(n: int, a: int = ALIGN) -> int:
+    return (n + a - 1) // a * a
+
+
+def required_bytes(specs) -> int:
+    """Heap bytes needed for ``specs`` = iterable of (shape, dtype), including the reserved region."""
+    total = RESERVED_BYTES
+    for shape, dtype in specs:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        total += _align(max(1, n * torch.empty((), dtype=dtype).element_size()))
+    return total
+
+
+@dataclass
+class HeapTensor:
+    tensor: torch.Tensor   # local view
+    offset: int            # byte offset in the heap
+    nbytes: int
+
+
+class SymmetricHeap:
+    """``SymmetricHeap(group, nbytes, device)`` is collective over ``group``."""
+
+    def __init__(self, group, nbytes: int, device, transport: str = "auto", timeout_s: float = 2.0):
+        self.group = group
+        self.device = torch.device(device)
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.nbytes = _align(int(nbytes), 4096)
+        self.timeout_s = timeout_s
+        self.init_failure_reason = None
+        self._handle = None
+        self._cursor = RESERVED_BYTES
+        self._registry: dict[str, HeapTensor] = {}
+        self.peer_ptrs = [0] * self.world
+        self.mc_ptr = 0
+        on_gpu = self.device.type == "cuda"
+        if self.world > 1 and on_gpu:
+            self._init_torch_symm()
+        else:
+            # World of one, or CPU ranks: an ordinary allocation is "symmetric" trivially.
+            self.buffer = torch.zeros(self.nbytes, dtype=torch.uint8, device=self.device)
+            self.peer_ptrs = [self.buffer.data_ptr()] if self.world == 1 else [0] * self.world
+        if transport == "auto":
+            transport = "multimem" if self.mc_ptr else "p2p"
+        if transport == "multimem" and not self.mc_ptr:
+            raise RuntimeError("multimem transport requested but no multicast address is available"
+                               + (f" ({self.init_failure_reason})" if self.init_failure_reason else ""))
+        if transport not in ("multimem", "p2p"):
+            raise ValueError(f"unknown transport {transport!r}")
+        self.transport = transport
+        # Local (not symmetric) state: per-block epochs and the status words.
+        self.epochs = torch.zeros(_ext.NUM_SITES * _ext.MAX_BLOCKS, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(_ext.STATUS_WORDS, dtype=torch.int32, device=self.device)
+        self._ctx = None
+
+    # -- bring-up ---------------------------------------------------------------------------
+    def _init_torch_symm(self):
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            try:
+                symm_mem.enable_symm_mem_for_group(self.group.group_name)
+            except Exception:
+                pass  # newer versions need no opt-in
+            self.buffer = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+            self.buffer.zero_()
+            self._handle = symm_mem.rendezvous(self.buffer, self.group.group_name)
+            self.peer_ptrs = [int(p) for p in self._handle.buffer_ptrs]
+            self.mc_ptr = int(getattr(self._handle, "multicast_ptr", 0) or 0)
+            if not self.mc_ptr:
+                self.init_failure_reason = "no NVLS multicast object for this group"
+            torch.cuda.synchronize()
+            dist.barrier(self.group)
+        except Exception as e:  # surfaced by callers as a RuntimeError with the reason
+            self.init_failure_reason = f"{type(e).__name__}: {e}"
+            raise RuntimeError(f"symmetric heap bring-up failed: {self.init_failure_reason}") from e
+
+    # -- sub-allocation -----------------------------------------------------------------------
+    def alloc(self, key: str, shape, dtype) -> HeapTensor:
+        """Carve ``shape`` x ``dtype`` out of the heap under ``key``.  Every rank must call this
+        in the same order with the same sizes so offsets agree.  Re-using a key returns the
+        existing tensor if the size matches."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        esize = torch.empty((), dtype=dtype).element_size()
+        nbytes = max(1, n * esize)
+        if key in self._registry:
+            ht = self._registry[key]
+            if ht.nbytes != nbytes:
+                raise ValueError(f"heap key {key!r} exists with {ht.nbytes} bytes, asked for {nbytes}")
+            return ht
+        off = self._cursor
+        if off + nbytes > self.nbytes:
+            raise MemoryError(f"symmetric heap exhausted: {key!r} needs {nbytes} bytes at offset {off}, "
+                              f"heap has {self.nbytes}")
+        self._cursor = _align(off + nbytes)
+        view = self.buffer[off:off + n * esize].view(dtype).view(*shape)
+        ht = HeapTensor(view, off, nbytes)
+        self._registry[key] = ht
+        return ht
+
+    def get(self, key: str) -> HeapTensor:
+        return self._registry[key]
+
+    def bytes_used(self) -> int:
+        return self._cursor
+
+    @property
+    def flags_off(self) -> int:
+        return 0
+
+    @property
+    def counts_off(self) -> int:
+        return FLAGS_BYTES
+
+    def peer_view(self, peer: int, ht: HeapTensor) -> torch.Tensor:
+        """This rank's mapping of ``peer``'s copy of a heap tensor (debug / validation only)."""
+        if peer == self.rank:
+            return ht.tensor
+        if self._handle is None:
+            raise RuntimeError("no peer mappings on this heap")
+        esize = ht.tensor.element_size()
+        return self._handle.get_buffer(peer, tuple(ht.tensor.shape), ht.tensor.dtype, ht.offset // esize)
+
+    # -- kernel context -------------------------------------------------------------------------
+    def ctx(self) -> "_ext.McbCtx":
+        if self._ctx is None:
+            if self.world > _ext.MAX_RANKS:
+                raise ValueError(f"world {self.world} exceeds MCB_MAX_RANKS {_ext.MAX_RANKS}")
+            c = _ext.McbCtx()
+            c.rank, c.world = self.rank, self.world
+            c.transport = _ext.TRANSPORT_MULTIMEM if self.transport == "multimem" else _ext.TRANSPORT_P2P
+            c.timeout_ns = int(self.timeout_s * 1e9)
+            c.heap_local = self.buffer.data_ptr()
+            c.heap_mc = self.mc_ptr
+            c.flags_off = self.flags_off
+            c.epochs = self.epochs.data_ptr()
+            c.status = self.status.data_ptr()
+            for p in range(self.world):
+                c.heap_peer[p] = self.peer_ptrs[p]
+            self._ctx = c
+        return self._ctx
+
+    def set_timeout(self, seconds: float):
+        self.timeout_s = seconds
+        self._ctx = None
+
+    # -- health ------------------------------------------------------------------------------------
+    def read_status(self) -> list[int]:
+        return [int(v) & 0xFFFFFFFF for v in self.status.cpu().tolist()]
+
+    def check_status(self):
+        """Host-synchronising health check: raises ``DeviceStatusError`` if a kernel on this rank
+        recorded an error.  The status words are cleared so the heap can be reused after
+        ``reset_sync_state``."""
+        words = self.read_status()
+        if words[0] != 0:
+            self.status.zero_()
+            raise DeviceStatusError(words)
+
+    def reset_sync_state(self):
+        """Collective: zero the flags and epochs on every rank (after an error, or between
+        tests).  All kernels must have drained."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(self.group)
+        self.buffer[:RESERVED_BYTES].zero_()
+        self.epochs.zero_()
+        self.status.zero_()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(self.group)
+
+    def destroy(self):
+        self._registry.clear()
+        self._handle = None
+        self.buffer = None
+
+
+class SymmetricHeapManager:
+    """Keyed registry of heaps (role of SymmetricMemoryManager, symmetric_memory.py:133-184)."""
+
+    _heaps: dict[str, SymmetricHeap] = {}
+
+    @classmethod
+    def get_heap(cls, key: str, group=None, nbytes: int = 512 << 20, device=None, **kw) -> SymmetricHeap:
+        if key not in cls._heaps:
+            if device is None:
+                device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() \
+                    else torch.device("cpu")
+            cls._heaps[key] = SymmetricHeap(group, nbytes, device, **kw)
+        return cls._heaps[key]
+
+    @classmethod
+    def destroy(cls, key: str | None = None):
+        keys = [key] if key is not None else list(cls._heaps)
+        for k in keys:
+            h = cls._heaps.pop(k, None)
+            if h is not None:
+                h.destroy()
+
+    @classmethod
+    def is_initialized(cls, key: str) -> bool:
+        return key in cls._heaps

@@ -1,0 +1,63 @@
+"""Background sampling of SM clocks and throttle reasons with ``nvidia-smi`` while a timed
+region runs.  Read-only: nothing here changes a GPU setting."""
+from __future__ import annotations
+
+import shutil
+import statistics
+import subprocess
+import tempfile
+
+_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+_REASONS = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+
+class ClockSampler:
+    def __init__(self, gpu_index: int = 0, period_ms: int = 200):
+        self.gpu_index, self.period_ms = gpu_index, period_ms
+        self._proc = None
+        self._file = None
+
+    def start(self):
+        exe = shutil.which("nvidia-smi")
+        if exe is None:
+            return self
+        self._file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self._proc = subprocess.Popen(
+            [exe, f"--query-gpu={_QUERY}", "--format=csv,noheader,nounits", "-lms", str(self.period_ms),
+             "-i", str(self.gpu_index)], stdout=self._file, stderr=subprocess.DEVNULL)
+        return self
+
+    def stop(self) -> dict:
+        if self._proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self._proc.terminate()      # the exact process started above
+        try:
+            self._proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self._proc.kill()
+        self._file.flush()
+        self._file.seek(0)
+        return parse_samples(self._file.read())
+
+
+def parse_samples(text: str) -> dict:
+    sm, mx, power, reasons = [], [], [], set()
+    for line in text.splitlines():
+        parts = [p.strip() for p in line.split(",")]
+        if len(parts) < 9:
+            continue
+        try:
+            sm.append(float(parts[1]))
+            mx.append(float(parts[2]))
+            power.append(float(parts[3]))
+        except ValueError:
+            continue
+        for name, val in zip(_REASONS, parts[5:9]):
+            if val.lower().startswith("active"):
+                reasons.add(name)
+    if not sm:
+        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+    return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "power_w_max": max(power),
+            "reasons": sorted(reasons), "samples": len(sm)}
