@@ -1,0 +1,184 @@
+"""Single-GPU emulation of a multi-rank world.
+
+All ranks of a collective run inside ONE cooperative kernel launch (grid.y = world), each
+y-slice with its own context, heap, epochs and status words; "peer" pointers are simply the
+other ranks' heaps on the same device.  This exercises the multi-rank protocol (offsets,
+barriers, slot maps, counts) where only one GPU is available.  Separate launches per rank
+would not do: kernels that wait on one another are never guaranteed to run concurrently.
+Only the peer-access transport can be emulated (a multicast address needs real NVSwitch
+members).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ..ops import _ext
+from .symm_heap import ALIGN, FLAGS_BYTES, RESERVED_BYTES, DeviceStatusError, HeapTensor, _align
+
+
+def _to_device(structs, device) -> torch.Tensor:
+    arr = (type(structs[0]) * len(structs))(*structs)
+    return torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8).to(device)
+
+
+class EmuWorld:
+    def __init__(self, world: int, heap_bytes: int, device="cuda:0", timeout_s: float = 2.0,
+                 phantom_ranks: int = 0):
+        """``phantom_ranks`` extra ranks are counted in ``world`` but never run: barriers can then
+        never complete, which is how the bounded-wait error path is exercised."""
+        self.world, self.device = world, torch.device(device)
+        self.total = world + phantom_ranks
+        self.nbytes = _align(heap_bytes + RESERVED_BYTES, 4096)
+        self.heaps = [torch.zeros(self.nbytes, dtype=torch.uint8, device=self.device) for _ in range(self.total)]
+        self.epochs = [torch.zeros(_ext.NUM_SITES * _ext.MAX_BLOCKS, dtype=torch.int32, device=self.device)
+                       for _ in range(world)]
+        self.status = [torch.zeros(_ext.STATUS_WORDS, dtype=torch.int32, device=self.device) for _ in range(world)]
+        self._cursor = RESERVED_BYTES
+        self.ctxs = []
+        for r in range(world):
+            c = _ext.McbCtx()
+            c.rank, c.world, c.transport = r, self.total, _ext.TRANSPORT_P2P
+            c.timeout_ns = int(timeout_s * 1e9)
+            c.heap_local, c.heap_mc, c.flags_off = self.heaps[r].data_ptr(), 0, 0
+            c.epochs, c.status = self.epochs[r].data_ptr(), self.status[r].data_ptr()
+            for p in range(self.total):
+                c.heap_peer[p] = self.heaps[p].data_ptr()
+            self.ctxs.append(c)
+        self.d_ctx = _to_device(self.ctxs, self.device)
+        self.counts_off = FLAGS_BYTES
+
+    def alloc(self, shape, dtype) -> list[HeapTensor]:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        esize = torch.empty((), dtype=dtype).element_size()
+        off = self._cursor
+        if off + n * esize > self.nbytes:
+            raise MemoryError("emulated heap exhausted")
+        self._cursor = _align(off + max(1, n * esize), ALIGN)
+        return [HeapTensor(h[off:off + n * esize].view(dtype).view(*shape), off, n * esize) for h in self.heaps]
+
+    def upload(self, structs) -> torch.Tensor:
+        return _to_device(structs, self.device)
+
+    def check_status(self):
+        for r in range(self.world):
+            words = [int(v) & 0xFFFFFFFF for v in self.status[r].cpu().tolist()]
+            if words[0]:
+                raise DeviceStatusError(words)
+
+    # ---- collectives over all emulated ranks -------------------------------------------------------
+    def _stream(self):
+        return _ext.stream_handle()
+
+    def metadata(self, n_locals, step_metas, cap):
+        args = []
+        for r in range(self.world):
+            a = _ext.McbMetaArgs()
+            a.n_local, a.counts_off, a.step_meta, a.cap = n_locals[r].data_ptr(), self.counts_off, step_metas[r].data_ptr(), cap
+            args.append(a)
+        d = self.upload(args)
+        _ext.check(_ext.require().mcb_emu_metadata(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
+                                                   self.world, self._stream()), "emu metadata")
+        torch.cuda.synchronize()
+
+    def all_gather_v(self, dsts, srcs, n_locals, step_metas, cap, grid=4, threads=256, site=_ext.SITE_AGV):
+        """dsts: list over tensors of per-rank HeapTensor lists; srcs: list over tensors of per-rank tensors."""
+        args = []
+        for r in range(self.world):
+            a = _ext.McbAgvArgs()
+            for i in range(len(srcs)):
+                a.src[i], a.dst_off[i] = srcs[i][r].data_ptr(), dsts[i][r].offset
+                a.row_bytes[i] = srcs[i][r].shape[1] * srcs[i][r].element_size()
+            a.num_tensors, a.cap, a.site = len(srcs), cap, site
+            a.n_local, a.step_meta = n_locals[r].data_ptr(), step_metas[r].data_ptr()
+            args.append(a)
+        d = self.upload(args)
+        _ext.check(_ext.require().mcb_emu_agv(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
+                                              self.world, grid, threads, self._stream()), "emu agv")
+        torch.cuda.synchronize()
+
+    def reduce_scatter_v(self, outs, src, n_locals, step_metas, cap, grid=4, threads=256, site=_ext.SITE_RSV):
+        args = []
+        for r in range(self.world):
+            a = _ext.McbRsvArgs()
+            a.out, a.src_off = outs[r].data_ptr(), src[r].offset
+            a.row_bytes = outs[r].shape[1] * outs[r].element_size()
+            a.dtype = 1 if outs[r].dtype == torch.float32 else 0
+            a.cap, a.site = cap, site
+            a.n_local, a.step_meta = n_locals[r].data_ptr(), step_metas[r].data_ptr()
+            args.append(a)
+        d = self.upload(args)
+        _ext.check(_ext.require().mcb_emu_rsv(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
+                                              self.world, grid, threads, self._stream()), "emu rsv")
+        torch.cuda.synchronize()
+
+    def barrier_test(self, grid=2, rounds=1):
+        _ext.check(_ext.require().mcb_emu_barrier_test(C.c_void_p(self.d_ctx.data_ptr()), self.world, grid, rounds,
+                                                       self._stream()), "emu barrier test")
+        torch.cuda.synchronize()
+
+    def a2a_buffers(self, cap, hidden, topk, fp8):
+        w = self.world
+        b = {"cap": cap, "hidden": hidden, "topk": topk, "fp8": fp8}
+        if fp8:
+            b["recv_x"] = self.alloc([w, cap, hidden], torch.uint8)
+            b["recv_scale"] = self.alloc([w, cap, hidden // 128], torch.float32)
+            b["y"] = self.alloc([w, cap, hidden], torch.bfloat16)
+        else:
+            b["recv_x"] = self.alloc([w, cap, hidden], torch.bfloat16)
+            b["recv_scale"] = None
+            b["y"] = b["recv_x"]
+        b["recv_idx"] = self.alloc([w, cap, topk], torch.int64)
+        b["recv_w"] = self.alloc([w, cap, topk], torch.float32)
+        b["recv_src"] = self.alloc([w, cap], torch.int32)
+        b["recv_count"] = self.alloc([_ext.MAX_RANKS], torch.int32)
+        b["slot_map"] = [torch.full((cap, w), -1, dtype=torch.int32, device=self.device) for _ in range(w)]
+        b["send_count"] = [torch.zeros(_ext.MAX_RANKS + 1, dtype=torch.int32, device=self.device) for _ in range(w)]
+        return b
+
+    def a2a_dispatch(self, b, xs, idxs, ws, n_locals, num_experts, grid=4, threads=256):
+        args = []
+        for r in range(self.world):
+            a = _ext.McbA2ADispatchArgs()
+            a.x, a.topk_idx, a.topk_w = xs[r].data_ptr(), idxs[r].data_ptr(), ws[r].data_ptr()
+            a.recv_x_off = b["recv_x"][r].offset
+            a.recv_scale_off = b["recv_scale"][r].offset if b["recv_scale"] else 0
+            a.recv_idx_off, a.recv_w_off = b["recv_idx"][r].offset, b["recv_w"][r].offset
+            a.recv_src_off, a.recv_count_off = b["recv_src"][r].offset, b["recv_count"][r].offset
+            a.slot_map, a.send_count = b["slot_map"][r].data_ptr(), b["send_count"][r].data_ptr()
+            a.n_local = n_locals[r].data_ptr()
+            a.hidden, a.topk, a.num_experts, a.cap, a.fp8 = b["hidden"], b["topk"], num_experts, b["cap"], int(b["fp8"])
+            args.append(a)
+        d = self.upload(args)
+        _ext.check(_ext.require().mcb_emu_a2a_dispatch(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
+                                                       self.world, grid, threads, self._stream()), "emu a2a dispatch")
+        torch.cuda.synchronize()
+
+    def a2a_combine(self, b, outs, n_locals, grid=4, threads=256):
+        args = []
+        for r in range(self.world):
+            a = _ext.McbA2ACombineArgs()
+            a.out, a.y_off = outs[r].data_ptr(), b["y"][r].offset
+            a.slot_map, a.n_local = b["slot_map"][r].data_ptr(), n_locals[r].data_ptr()
+            a.hidden, a.cap = b["hidden"], b["cap"]
+            args.append(a)
+        d = self.upload(args)
+        _ext.check(_ext.require().mcb_emu_a2a_combine(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
+                                                      self.world, grid, threads, self._stream()), "emu a2a combine")
+        torch.cuda.synchronize()
+
+    def rs_add_norm_ag(self, buf, residuals, weight, eps, grid=4):
+        tokens, hidden = buf[0].tensor.shape
+        args = []
+        for r in range(self.world):
+            a = _ext.McbNormArgs()
+            a.buf_off, a.residual, a.weight = buf[r].offset, residuals[r].data_ptr(), weight.data_ptr()
+            a.eps, a.hidden, a.tokens = eps, hidden, tokens
+            args.append(a)
+        d = self.upload(args)
+        _ext.check(_ext.require().mcb_emu_rs_add_norm_ag(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
+                                                         self.world, hidden, grid, self._stream()), "emu norm")
+        torch.cuda.synchronize()

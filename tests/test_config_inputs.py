@@ -1,0 +1,88 @@
+"""Token split, seeded generators, shape presets (CPU)."""
+import pytest
+import torch
+
+from moe_comms_benchmarking_b200.config import Config
+from moe_comms_benchmarking_b200.models.presets import get_preset
+from moe_comms_benchmarking_b200.parallel.dist import all_rank_counts, local_token_count
+from moe_comms_benchmarking_b200.utils.inputs import make_inputs, rank_counts, size_mb
+
+
+def test_balanced_split():
+    assert all_rank_counts(10, 4) == [3, 3, 2, 2]
+    assert all_rank_counts(1, 4) == [1, 0, 0, 0]
+    assert all_rank_counts(0, 3) == [0, 0, 0]
+    for b in (1, 7, 64, 8191):
+        for w in (1, 2, 4, 8):
+            c = all_rank_counts(b, w)
+            assert sum(c) == b and max(c) - min(c) <= 1
+            assert c[0] == local_token_count(b, 0, w)
+
+
+def test_config_properties_and_checks():
+    cfg = Config(ep_size=8, per_rank_cap=16)
+    assert cfg.num_local_experts == 64 and cfg.global_cap == 128
+    with pytest.raises(ValueError):
+        Config(num_experts=10, ep_size=4)
+    with pytest.raises(ValueError):
+        Config(num_experts=4, topk=8)
+
+
+def test_presets():
+    n = get_preset("nemotron-super")
+    assert (n.num_experts, n.topk, n.hidden, n.num_layers) == (512, 22, 1024, 88)
+    d = get_preset("deepseek-v3")
+    assert (d.num_experts, d.topk, d.hidden, d.num_layers, d.probs) == (256, 8, 7168, 58, "sigmoid")
+    with pytest.raises(ValueError):
+        get_preset("nope")
+
+
+def test_make_inputs_contract():
+    cfg = Config(num_experts=64, topk=6, hidden=32, ep_size=2, rank=1, per_rank_cap=8)
+    h, i, w = make_inputs(cfg, 9, "cpu")
+    assert h.shape == (4, 32) and h.dtype == torch.bfloat16
+    assert i.shape == (4, 6) and i.dtype == torch.int64
+    assert w.dtype == torch.float32
+    assert torch.allclose(w.sum(-1), torch.ones(4), atol=1e-5)
+    for row in i.tolist():
+        assert len(set(row)) == 6 and all(0 <= e < 64 for e in row)
+    h2, i2, w2 = make_inputs(cfg, 9, "cpu")
+    assert torch.equal(h, h2) and torch.equal(i, i2) and torch.equal(w, w2)
+    cfg0 = Config(num_experts=64, topk=6, hidden=32, ep_size=2, rank=0, per_rank_cap=8)
+    assert not torch.equal(make_inputs(cfg0, 9, "cpu")[1][:4], i)       # per-rank seed
+    e = make_inputs(cfg, 1, "cpu")                                       # rank 1 idle at B=1
+    assert e[0].shape == (0, 32) and e[1].shape == (0, 6) and e[2].shape == (0, 6)
+
+
+def test_zipf_routing_is_skewed_and_distinct():
+    cfg = Config(num_experts=128, topk=8, hidden=16, ep_size=1, per_rank_cap=512, routing="zipf")
+    _, idx, _ = make_inputs(cfg, 512, "cpu")
+    for row in idx.tolist():
+        assert len(set(row)) == 8
+    hist = torch.bincount(idx.flatten(), minlength=128).float()
+    top = hist.sort(descending=True).values
+    assert top[:8].sum() > 3 * top[-8:].sum()          # heavy head
+    cfgu = Config(num_experts=128, topk=8, hidden=16, ep_size=1, per_rank_cap=512)
+    histu = torch.bincount(make_inputs(cfgu, 512, "cpu")[1].flatten(), minlength=128).float()
+    assert hist.max() > 2 * histu.max()
+
+
+def test_sigmoid_probs_normalised():
+    cfg = Config(num_experts=32, topk=4, hidden=16, probs="sigmoid", per_rank_cap=8)
+    _, _, w = make_inputs(cfg, 8, "cpu")
+    assert torch.allclose(w.sum(-1), torch.ones(8), atol=1e-5) and (w > 0).all()
+
+
+def test_multinomial_counts_have_an_idle_rank():
+    cfg = Config(ep_size=8, per_rank_cap=8192, counts="multinomial")
+    for b in (1, 8, 256, 8192):
+        c = rank_counts(cfg, b)
+        assert sum(c) == b and min(c) == 0 and len(c) == 8
+        assert c == rank_counts(cfg, b)
+    assert rank_counts(Config(ep_size=4, per_rank_cap=4), 10) == [3, 3, 2, 2]
+
+
+def test_size_mb():
+    assert size_mb([1], torch.int32) == 1
+    assert size_mb([1024, 1024], torch.bfloat16) == 2
+    assert size_mb([1024, 1025], torch.bfloat16) == 3

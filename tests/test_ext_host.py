@@ -1,0 +1,119 @@
+"""Library build, struct layouts and host-side argument validation (CPU: nothing is launched)."""
+import ctypes as C
+
+import pytest
+import torch
+
+from moe_comms_benchmarking_b200.ops import _ext
+from moe_comms_benchmarking_b200.ops.a2a import A2ABuffers, A2ACombinePlan, A2ADispatchPlan
+from moe_comms_benchmarking_b200.ops.dense import AllGatherVPlan, MetadataPlan, ReduceScatterVPlan
+from moe_comms_benchmarking_b200.ops.norm import RsAddNormAgPlan
+from moe_comms_benchmarking_b200.parallel.symm_heap import (RESERVED_BYTES, DeviceStatusError, SymmetricHeap,
+                                                            SymmetricHeapManager, required_bytes)
+
+
+def test_library_builds_and_layouts_match(lib):
+    assert lib.mcb_max_ranks() == _ext.MAX_RANKS
+    assert lib.mcb_max_blocks() == _ext.MAX_BLOCKS
+    assert lib.mcb_num_sites() == _ext.NUM_SITES
+    assert lib.mcb_sizeof_ctx() == C.sizeof(_ext.McbCtx)
+
+
+def _heap(nbytes=1 << 20):
+    return SymmetricHeap(None, nbytes, "cpu")
+
+
+def test_heap_bump_allocator_and_registry():
+    h = _heap()
+    a = h.alloc("a", [10, 3], torch.float32)
+    b = h.alloc("b", [7], torch.int64)
+    assert a.offset == RESERVED_BYTES and a.offset % 256 == 0 and b.offset % 256 == 0
+    assert b.offset >= a.offset + a.nbytes
+    assert h.alloc("a", [10, 3], torch.float32) is a
+    with pytest.raises(ValueError):
+        h.alloc("a", [11, 3], torch.float32)
+    with pytest.raises(MemoryError):
+        h.alloc("huge", [1 << 22], torch.float32)
+    a.tensor.fill_(3.0)
+    assert h.buffer[a.offset:a.offset + 4].view(torch.float32).item() == 3.0
+    assert required_bytes([([10, 3], torch.float32), ([7], torch.int64)]) == RESERVED_BYTES + 256 + 256
+    c = h.ctx()
+    assert c.world == 1 and c.rank == 0 and c.transport == _ext.TRANSPORT_P2P
+    assert c.heap_peer[0] == c.heap_local == h.buffer.data_ptr()
+
+
+def test_heap_manager_registry():
+    SymmetricHeapManager.destroy()
+    assert not SymmetricHeapManager.is_initialized("k")
+    h = SymmetricHeapManager.get_heap("k", None, 1 << 16, device="cpu")
+    assert SymmetricHeapManager.get_heap("k") is h and SymmetricHeapManager.is_initialized("k")
+    SymmetricHeapManager.destroy("k")
+    assert not SymmetricHeapManager.is_initialized("k")
+
+
+def test_multimem_transport_needs_multicast():
+    with pytest.raises(RuntimeError):
+        SymmetricHeap(None, 1 << 16, "cpu", transport="multimem")
+
+
+def test_status_error_decoding():
+    e = DeviceStatusError([1, 2, 7, 5, 8, 3, 0, 0])
+    assert e.code == 1 and "timeout" in str(e) and "site 2 block 7 on rank 3" in str(e)
+
+
+def test_dense_plans_validate_arguments():
+    h = _heap(4 << 20)
+    cap, H, K = 8, 64, 6
+    n_local = torch.zeros(1, dtype=torch.int32)
+    meta = torch.zeros(4, dtype=torch.int32)
+    gh = h.alloc("gh", [cap, H], torch.bfloat16)
+    gr = h.alloc("gr", [cap, K], torch.int64)
+    src_h = torch.zeros(cap, H, dtype=torch.bfloat16)
+    src_r = torch.zeros(cap, K, dtype=torch.int64)
+    MetadataPlan(h, n_local, meta, cap)
+    with pytest.raises(ValueError):
+        MetadataPlan(h, torch.zeros(1, dtype=torch.int64), meta, cap)
+    AllGatherVPlan(h, [gh, gr], [src_h, src_r], n_local, meta, cap)
+    with pytest.raises(ValueError):      # source smaller than capacity
+        AllGatherVPlan(h, [gh], [src_h[:4]], n_local, meta, cap)
+    with pytest.raises(ValueError):      # gathered buffer too small
+        AllGatherVPlan(h, [gh], [src_h], n_local, meta, cap * 2)
+    with pytest.raises(ValueError):      # dtype mismatch
+        AllGatherVPlan(h, [gh], [src_h.float()], n_local, meta, cap)
+    with pytest.raises(ValueError):      # row not a multiple of 4 bytes
+        odd = h.alloc("odd", [cap, 3], torch.uint8)
+        AllGatherVPlan(h, [odd], [torch.zeros(cap, 3, dtype=torch.uint8)], n_local, meta, cap)
+    with pytest.raises(ValueError):      # grid beyond the flag slots
+        AllGatherVPlan(h, [gh], [src_h], n_local, meta, cap, grid=_ext.MAX_BLOCKS + 1)
+    out = torch.zeros(cap, H, dtype=torch.bfloat16)
+    ReduceScatterVPlan(h, out, gh, n_local, meta, cap)
+    with pytest.raises(ValueError):      # rows must be multiples of 16 bytes
+        g6 = h.alloc("g6", [cap, 6], torch.bfloat16)
+        ReduceScatterVPlan(h, torch.zeros(cap, 6, dtype=torch.bfloat16), g6, n_local, meta, cap)
+    with pytest.raises(ValueError):
+        ReduceScatterVPlan(h, out.float(), gh, n_local, meta, cap)
+
+
+def test_a2a_and_norm_plans_validate_arguments():
+    h = _heap(8 << 20)
+    cap, H, K = 4, 256, 4
+    bufs = A2ABuffers(h, cap, H, K, fp8=False)
+    assert bufs.y is bufs.recv_x
+    n_local = torch.zeros(1, dtype=torch.int32)
+    x = torch.zeros(cap, H, dtype=torch.bfloat16)
+    idx = torch.zeros(cap, K, dtype=torch.int64)
+    w = torch.ones(cap, K)
+    A2ADispatchPlan(h, bufs, x, idx, w, n_local, 16)
+    with pytest.raises(ValueError):
+        A2ADispatchPlan(h, bufs, x.float(), idx, w, n_local, 16)
+    with pytest.raises(ValueError):
+        A2ADispatchPlan(h, bufs, x, idx.int(), w, n_local, 16)
+    A2ACombinePlan(h, bufs, torch.zeros(cap, H, dtype=torch.bfloat16), n_local)
+    with pytest.raises(ValueError):
+        A2ABuffers(h, cap, 200, K, fp8=True, prefix="bad")
+    b8 = A2ABuffers(h, cap, H, K, fp8=True, prefix="f8")
+    assert b8.recv_scale.tensor.shape == (1, cap, 2) and b8.y is not b8.recv_x
+    buf = h.alloc("norm", [8, 64], torch.bfloat16)
+    RsAddNormAgPlan(h, buf, torch.zeros(8, 64, dtype=torch.bfloat16), torch.ones(64, dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        RsAddNormAgPlan(h, buf, torch.zeros(4, 64, dtype=torch.bfloat16), torch.ones(64, dtype=torch.bfloat16))
