@@ -35,13 +35,14 @@ struct DestList {
 
 __device__ __forceinline__ uint32_t warp_or(uint32_t v) { return __reduce_or_sync(0xffffffffu, v); }
 
-// Quantise 8 bf16 values (one 16-byte pack) with a given inverse scale to 8 e4m3 bytes.
-__device__ __forceinline__ uint2 quant_pack_e4m3(uint4 v, float inv_scale) {
+// Quantise 8 bf16 values (one 16-byte pack) to 8 e4m3 bytes: saturating RNE of v / scale.
+__device__ __forceinline__ uint2 quant_pack_e4m3(uint4 v, float scale) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
   uint16_t q[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 f = make_float2(bf16_lo(w[i]) * inv_scale, bf16_hi(w[i]) * inv_scale);
+    // true division (not a reciprocal multiply) so results match an fp32 reference bit for bit
+    const float2 f = make_float2(__fdiv_rn(bf16_lo(w[i]), scale), __fdiv_rn(bf16_hi(w[i]), scale));
     q[i] = (uint16_t)__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
   }
   return make_uint2((uint32_t)q[0] | ((uint32_t)q[1] << 16), (uint32_t)q[2] | ((uint32_t)q[3] << 16));
@@ -139,8 +140,8 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
         float amax = pack_absmax(v);
 #pragma unroll
         for (int s = 8; s >= 1; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
-        const float scale = amax > 0.f ? amax * (1.0f / 448.0f) : 1.0f;
-        const uint2 q = quant_pack_e4m3(v, 1.0f / scale);
+        const float scale = amax > 0.f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+        const uint2 q = quant_pack_e4m3(v, scale);
         const int blk = p >> 4;
         for (int j = 0; j < m; ++j) {
           const uint64_t row = (uint64_t)c.rank * a.cap + L.slot[j];
@@ -209,8 +210,8 @@ __global__ void __launch_bounds__(512) a2a_combine_kernel(const __grid_constant_
   if (n > a.cap) n = a.cap;
   const uint32_t ep = *epoch_ptr(c, MCB_SITE_A2A_COMBINE, blockIdx.x);
   // Leading barrier: every destination's expert outputs were written by kernels that
-  // finished before its block arrived here.
-  block_barrier_all(c, MCB_SITE_A2A_COMBINE, blockIdx.x, ep);
+  // finished before its block arrived here (no release fence needed).
+  block_barrier_all<false>(c, MCB_SITE_A2A_COMBINE, blockIdx.x, ep);
 
   const int row_packs = a.hidden / 8;
   const uint64_t row_bytes = (uint64_t)a.hidden * 2;

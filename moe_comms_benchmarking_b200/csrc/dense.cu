@@ -265,8 +265,8 @@ __global__ void __launch_bounds__(512) rsv_kernel(const __grid_constant__ McbCtx
     n = 0;
   }
   // Leading barrier: every rank's partial sums were written by kernels that finished before
-  // that rank's block arrived here.
-  block_barrier_all(c, a.site, bid, ep);
+  // that rank's block arrived here, so the arrival needs no release fence.
+  block_barrier_all<false>(c, a.site, bid, ep);
 
   const long long nvec = (long long)n * a.row_bytes / 16;
   const long long start = (long long)bid * blockDim.x + threadIdx.x;
@@ -287,10 +287,16 @@ __global__ void __launch_bounds__(512) rsv_kernel(const __grid_constant__ McbCtx
         if (i + u * stride < nvec) st_v4(out + (i + u * stride) * 16, v[u]);
     }
   } else {
-    for (long long i = start; i < nvec; i += stride) {
-      const uint4 v = a.dtype == 1 ? p2p_reduce_pack<true>(c, base + i * 16)
-                                   : p2p_reduce_pack<false>(c, base + i * 16);
-      st_v4(out + i * 16, v);
+    for (long long i = start; i < nvec; i += stride * kUnroll) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (i + u * stride < nvec)
+          v[u] = a.dtype == 1 ? p2p_reduce_pack<true>(c, base + (i + u * stride) * 16)
+                              : p2p_reduce_pack<false>(c, base + (i + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (i + u * stride < nvec) st_v4(out + (i + u * stride) * 16, v[u]);
     }
   }
 }

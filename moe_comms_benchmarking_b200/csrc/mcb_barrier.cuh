@@ -37,12 +37,20 @@ __device__ __forceinline__ uint32_t* epoch_ptr(const McbCtx& c, int site, int sl
 
 // Called by every thread of the block after a __syncthreads() that follows the block's
 // data writes.  Adds 1 to flag[site][slot] on every rank (self included).
+// RELEASE = false is for a barrier that only announces "the kernels before this one have
+// finished" (their writes were completed at the kernel boundary), so no fence is needed.
+template <bool RELEASE = true>
 __device__ __forceinline__ void signal_all(const McbCtx& c, int site, int slot) {
   if (c.transport == MCB_TRANSPORT_MULTIMEM) {
-    if (threadIdx.x == 0) mm_red_add_release(flag_ptr(c.heap_mc, c, site, slot), 1u);
+    if (threadIdx.x == 0) {
+      if (RELEASE) mm_red_add_release(flag_ptr(c.heap_mc, c, site, slot), 1u);
+      else mm_red_add_relaxed(flag_ptr(c.heap_mc, c, site, slot), 1u);
+    }
   } else {
-    for (int p = threadIdx.x; p < c.world; p += blockDim.x)
-      red_add_release_sys(flag_ptr(c.heap_peer[p], c, site, slot), 1u);
+    for (int p = threadIdx.x; p < c.world; p += blockDim.x) {
+      if (RELEASE) red_add_release_sys(flag_ptr(c.heap_peer[p], c, site, slot), 1u);
+      else red_add_relaxed_sys(flag_ptr(c.heap_peer[p], c, site, slot), 1u);
+    }
   }
 }
 
@@ -71,9 +79,11 @@ __device__ __forceinline__ bool wait_flag(const McbCtx& c, int site, int slot, u
 
 // Whole-block barrier with every other rank's block `slot`.  `ep` is the block's epoch
 // read earlier from epoch_ptr(); the epoch is advanced here.  Ends with __syncthreads().
+template <bool RELEASE = true>
 __device__ __forceinline__ void block_barrier_all(const McbCtx& c, int site, int slot, uint32_t ep) {
   __syncthreads();
-  signal_all(c, site, slot);
+  if (c.world == 1) return;  // nobody to meet: stream order alone orders a single rank's kernels
+  signal_all<RELEASE>(c, site, slot);
   if (threadIdx.x == 0) {
     wait_flag(c, site, slot, (ep + 1u) * (uint32_t)c.world);
     *epoch_ptr(c, site, slot) = ep + 1u;

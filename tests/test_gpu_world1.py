@@ -117,7 +117,11 @@ def test_uniform_collectives_world1(world1):
 
 
 def _run(cmd, timeout=600):
-    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, cwd=ROOT)
+    # children rendezvous on their own port, not on the one this process's group listens on
+    env = dict(os.environ, MASTER_PORT=str(free_port()))
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, cwd=ROOT, env=env)
 
 
 def test_driver_validate_and_sweep_one_gpu(tmp_path):
