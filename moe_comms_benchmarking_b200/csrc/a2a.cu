@@ -18,11 +18,13 @@
 //     destinations' expert-output buffers, accumulates in fp32 and writes bf16;
 //   * optional 1x128 block-scaled e4m3 dispatch: amax over each 128-element block, scale =
 //     amax / 448, saturating convert, fp32 scales shipped next to the rows.
+#include <cstdio>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include "mcb_barrier.cuh"
 #include "mcb_launch.h"
+#include "mcb_noalloc.h"
 
 namespace mcb {
 
@@ -320,6 +322,65 @@ int mcb_emu_a2a_combine(const McbCtx* d_ctx, const McbA2ACombineArgs* d_args, in
   McbA2ACombineArgs dargs{};
   return launch_kernel(a2a_combine_kernel<true>, dim3(grid, world), dim3(threads), 0, stream, 0, true, dummy,
                        dargs, d_ctx, d_args);
+}
+
+// ------------------------------------------------------------------------------------------
+// Dispatch for callers that cannot allocate (see mcb_noalloc.h).
+//
+// The per-destination slot counters and the "blocks done" word, which the ordinary entry
+// point expects the caller to provide in `send_count`, live here in a fixed array that is
+// part of the loaded library image: every GPU that loads the library holds these
+// MCB_NOALLOC_SCRATCH_BYTES bytes until the process exits.
+// ------------------------------------------------------------------------------------------
+static __device__ __align__(256) int32_t g_noalloc_send_count[MCB_NOALLOC_MAX_RANKS + 1];
+
+#define MCB_NOALLOC_MAX_DEVICES 64
+static int32_t* g_noalloc_scratch_addr[MCB_NOALLOC_MAX_DEVICES];   // device address, per device
+static char g_noalloc_error[256] = "";
+
+const char* mcb_noalloc_last_error() { return g_noalloc_error; }
+int mcb_noalloc_max_ranks() { return MCB_NOALLOC_MAX_RANKS; }
+int mcb_noalloc_scratch_bytes() { return MCB_NOALLOC_SCRATCH_BYTES; }
+
+int mcb_a2a_dispatch_noalloc(const McbCtx* ctx, const McbA2ADispatchArgs* args, int grid, int threads,
+                             cudaStream_t stream) {
+  g_noalloc_error[0] = 0;
+  if (ctx == nullptr || args == nullptr) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), "mcb_a2a_dispatch_noalloc: null context or arguments");
+    return cudaErrorInvalidValue;
+  }
+  if (ctx->world < 1 || ctx->world > MCB_NOALLOC_MAX_RANKS) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error),
+             "mcb_a2a_dispatch_noalloc: world size %d is outside [1, %d], the number of destination "
+             "counters the built-in scratch array holds", ctx->world, MCB_NOALLOC_MAX_RANKS);
+    return cudaErrorInvalidValue;
+  }
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return (int)err;
+  if (dev < 0 || dev >= MCB_NOALLOC_MAX_DEVICES) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), "mcb_a2a_dispatch_noalloc: device ordinal %d is beyond %d",
+             dev, MCB_NOALLOC_MAX_DEVICES);
+    return cudaErrorInvalidDevice;
+  }
+  if (g_noalloc_scratch_addr[dev] == nullptr) {
+    // In host code the array's name is only a stand-in; the kernel needs the address the
+    // symbol has on the current device.  Looked up once per device, on this first call.
+    void* p = nullptr;
+    err = cudaGetSymbolAddress(&p, g_noalloc_send_count);
+    if (err != cudaSuccess) {
+      snprintf(g_noalloc_error, sizeof(g_noalloc_error), "mcb_a2a_dispatch_noalloc: cudaGetSymbolAddress failed: %s",
+               cudaGetErrorString(err));
+      return (int)err;
+    }
+    g_noalloc_scratch_addr[dev] = static_cast<int32_t*>(p);
+  }
+  McbA2ADispatchArgs a = *args;
+  a.send_count = g_noalloc_scratch_addr[dev];
+  // The counters must start at zero; an earlier call that was cut short may have left them dirty.
+  err = cudaMemsetAsync(a.send_count, 0, sizeof(int32_t) * (MCB_NOALLOC_MAX_RANKS + 1), stream);
+  if (err != cudaSuccess) return (int)err;
+  return mcb_launch_a2a_dispatch(ctx, &a, grid, threads, 0, stream);
 }
 
 }  // extern "C"
