@@ -46,6 +46,7 @@ def parse_args(argv=None):
     p.add_argument("--global-batch", type=int, default=8192)
     p.add_argument("--sweep", default="1,64,512,4096", help="extra global batches reported under 'sweep'")
     p.add_argument("--no-pdl", action="store_true")
+    p.add_argument("--ll-rows", type=int, default=768)
     return p.parse_args(argv)
 
 
@@ -93,7 +94,8 @@ def run_native(args):
     B = args.global_batch
     sweep = [int(b) for b in args.sweep.split(",") if b.strip()]
     cfg = Config(ep_size=world, rank=rank, local_rank=local_rank, per_rank_cap=-(-max([B] + sweep) // world))
-    eng = MoEDecodeEngine(cfg, group, impl=args.native_impl, num_layers=NUM_LAYERS, pdl=not args.no_pdl).build()
+    kw = {"ll_rows": args.ll_rows} if args.native_impl == "dense" else {}
+    eng = MoEDecodeEngine(cfg, group, impl=args.native_impl, num_layers=NUM_LAYERS, pdl=not args.no_pdl, **kw).build()
     eng.capture()
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
@@ -133,7 +135,8 @@ def run_native(args):
                        "global_batch": B, "seq_len": 1, "parallelism": f"ep{world}",
                        "per_rank_tokens": all_rank_counts(B, world), "transport": eng.dispatcher.heap.transport,
                        "timing": "one CUDA graph per step; L2 flushed between steps (256 MiB write)",
-                       "pdl": not args.no_pdl, "num_sms": eng.dispatcher.num_sms},
+                       "pdl": not args.no_pdl, "num_sms": eng.dispatcher.num_sms,
+                       "low_latency_max_global_rows": getattr(eng.dispatcher, "ll_rows", 0)},
             "e2e": {"value": round(e2e_ms, 4), "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
             "sweep_ms_by_global_batch": {k: round(v, 4) for k, v in sweep_ms.items()},

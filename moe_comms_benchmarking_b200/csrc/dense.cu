@@ -148,27 +148,150 @@ __device__ __forceinline__ int active_blocks(int grid, int ep_max, long long byt
   return nb < grid ? nb : grid;
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Low-latency packets.  A packet is 16 bytes {data.lo, flag, data.hi, flag}: 8 bytes of payload
+// and the launch's flag value twice, so each 8-byte half carries its own flag and the packet is
+// valid as soon as both flags match (the scheme of NCCL's LL protocol).  The flag changes with
+// every launch, so a packet left over from an earlier launch is never mistaken for a new one.
+// ------------------------------------------------------------------------------------------
+constexpr int kLLBlocks = 128;
+
+__device__ __forceinline__ uint4 ll_pack(uint2 d, uint32_t flag) { return make_uint4(d.x, flag, d.y, flag); }
+
+// Poll one packet in local memory until it carries `flag`.  Bounded; on timeout records the
+// error and returns zeros.
+__device__ __forceinline__ uint2 ll_wait(const McbCtx& c, const uint8_t* slot, uint32_t flag, int site) {
+  uint4 v = ld_v4_volatile(slot);
+  if (v.y == flag && v.w == flag) return make_uint2(v.x, v.z);
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      v = ld_v4_volatile(slot);
+      if (v.y == flag && v.w == flag) return make_uint2(v.x, v.z);
+    }
+    const bool poisoned = *reinterpret_cast<volatile uint32_t*>(c.status) != 0u;
+    if (poisoned || globaltimer_ns() - t0 > c.timeout_ns) {
+      report_error(c, MCB_ERR_TIMEOUT, (uint32_t)site, blockIdx.x, v.y, flag);
+      return make_uint2(0u, 0u);
+    }
+  }
+}
+
+// Every block of every launch advances its own launch counter, whether it has work or not, so
+// the counters (and with them flag and parity) agree across blocks and ranks.
+__device__ __forceinline__ uint32_t ll_next_flag(const McbCtx& c, int site) {
+  uint32_t* ctr = epoch_ptr(c, site, blockIdx.x);
+  const uint32_t v = *ctr + 1u;
+  __syncthreads();
+  if (threadIdx.x == 0) *ctr = v;
+  return v;
+}
+
+__device__ __forceinline__ bool agv_ll_eligible(const McbCtx& c, const McbAgvArgs& a, int valid) {
+  if (c.world == 1 || a.ll_rows <= 0 || valid <= 0 || valid > a.ll_rows) return false;
+  bool ok = true;
+#pragma unroll
+  for (int t = 0; t < MCB_MAX_TENSORS; ++t)
+    if (t < a.num_tensors && (a.row_bytes[t] & 7u)) ok = false;
+  return ok;
+}
+
+// Low-latency all-gather-V: send my rows as packets to every rank's staging area, then poll my
+// own staging area for all `valid` rows and unpack them into the gathered tensors.
+__device__ __forceinline__ void agv_ll(const McbCtx& c, const McbAgvArgs& a, int n, int offset, int valid,
+                                       uint32_t flag) {
+  int w[MCB_MAX_TENSORS];
+  int wpr = 0;
+#pragma unroll
+  for (int t = 0; t < MCB_MAX_TENSORS; ++t) {
+    w[t] = t < a.num_tensors ? (int)(a.row_bytes[t] >> 3) : 0;
+    wpr += w[t];
+  }
+  const uint64_t stage = a.ll_off + (uint64_t)(flag & 1u) * a.ll_rows * wpr * 16;
+  // Blocks poll for packets that other ranks' blocks send, so every taking-part block must be
+  // resident at the same time: at most kLLBlocks of them (one per SM always fits).
+  const int nb = (int)gridDim.x < kLLBlocks ? (int)gridDim.x : kLLBlocks;
+  if ((int)blockIdx.x >= nb) return;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)nb * blockDim.x;
+  // send
+  for (long long i = tid; i < (long long)n * wpr; i += nthreads) {
+    const int row = (int)(i / wpr);
+    int j = (int)(i - (long long)row * wpr);
+    const int jj = j;
+    int t = 0;
+#pragma unroll
+    for (int k = 0; k < MCB_MAX_TENSORS - 1; ++k)
+      if (t == k && j >= w[k]) { j -= w[k]; t = k + 1; }
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.src[t]) + (uint64_t)row * a.row_bytes[t] + (uint64_t)j * 8;
+    const uint4 pkt = ll_pack(ld_v2(src), flag);
+    const uint64_t off = stage + ((uint64_t)(offset + row) * wpr + jj) * 16;
+    if (c.transport == MCB_TRANSPORT_MULTIMEM) {
+      mm_st_v4(c.heap_mc + off, pkt);
+    } else {
+      for (int k = 0; k < c.world; ++k) {
+        int p = c.rank + 1 + k;
+        if (p >= c.world) p -= c.world;
+        st_v4(c.heap_peer[p] + off, pkt);
+      }
+    }
+  }
+  // receive
+  for (long long i = tid; i < (long long)valid * wpr; i += nthreads) {
+    const int row = (int)(i / wpr);
+    int j = (int)(i - (long long)row * wpr);
+    const uint2 d = ll_wait(c, c.heap_local + stage + (uint64_t)i * 16, flag, a.site);
+    int t = 0;
+#pragma unroll
+    for (int k = 0; k < MCB_MAX_TENSORS - 1; ++k)
+      if (t == k && j >= w[k]) { j -= w[k]; t = k + 1; }
+    st_v2(c.heap_local + a.dst_off[t] + (uint64_t)row * a.row_bytes[t] + (uint64_t)j * 8, d);
+  }
+}
+
 template <bool EMU>
 __global__ void __launch_bounds__(512) agv_kernel(const __grid_constant__ McbCtx ctx_p,
                                                    const __grid_constant__ McbAgvArgs args_p,
                                                    const McbCtx* ectx, const McbAgvArgs* eargs) {
   const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
   const McbAgvArgs& a = EMU ? eargs[blockIdx.y] : args_p;
-  pdl_wait();
   const int bid = blockIdx.x;
-  int n = *a.n_local;
-  const int offset = a.step_meta[1];
-  const int ep_max = a.step_meta[2];
+  int n = 0, valid_pre = 0, offset = 0, ep_max = 0;
+  if (a.meta_stable) {
+    n = *a.n_local;
+    valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2];
+  }
+  pdl_wait();
+  if (!a.meta_stable) {
+    n = *a.n_local;
+    valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2];
+  }
   long long bytes_per_row = 0;
 #pragma unroll
   for (int t = 0; t < MCB_MAX_TENSORS; ++t)
     if (t < a.num_tensors) bytes_per_row += a.row_bytes[t];
   const int nact = active_blocks((int)gridDim.x, ep_max, bytes_per_row, (int)blockDim.x);
   pdl_launch_dependents();
+  const bool bad = n < 0 || n > a.cap || offset < 0 || (long long)offset + n > (long long)a.cap * c.world;
+  if (a.ll_rows > 0 && c.world > 1) {
+    // The launch counter advances on every launch, in either mode.
+    const uint32_t flag = ll_next_flag(c, MCB_SITE_AGV_LL);
+    if (agv_ll_eligible(c, a, valid_pre)) {
+      const int valid = valid_pre;
+      if (bad) {
+        if (threadIdx.x == 0) report_error(c, MCB_ERR_BOUNDS, (uint32_t)a.site, (uint32_t)bid, (uint32_t)n, (uint32_t)valid);
+        return;
+      }
+      agv_ll(c, a, n, offset, valid, flag);
+      return;
+    }
+  }
   if (bid >= nact) return;
   const uint32_t ep = *epoch_ptr(c, a.site, bid);
   if (n < 0) n = 0;
-  if (n > a.cap || offset < 0 || (long long)offset + n > (long long)a.cap * c.world) {
+  if (bad) {
     if (threadIdx.x == 0)
       report_error(c, n > a.cap ? MCB_ERR_CAPACITY : MCB_ERR_BOUNDS, (uint32_t)a.site, (uint32_t)bid,
                    (uint32_t)n, (uint32_t)offset);
@@ -242,23 +365,89 @@ __device__ __forceinline__ uint4 p2p_reduce_pack(const McbCtx& c, uint64_t off) 
                     pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
 }
 
+
+// Low-latency reduce-scatter-V (bf16): push every valid row of my partial sums to its owner as
+// packets, then sum, for each of my own rows, the packets of all ranks in rank order (fp32).
+__device__ __forceinline__ void rsv_ll(const McbCtx& c, const McbRsvArgs& a, int n, int offset, int valid,
+                                       uint32_t flag, const int* s_prefix) {
+  const int wpr = (int)(a.row_bytes >> 3);
+  const uint64_t per_src = (uint64_t)a.ll_src_rows * wpr * 16;
+  const uint64_t stage = a.ll_off + (uint64_t)(flag & 1u) * c.world * per_src;
+  const int nb = (int)gridDim.x < kLLBlocks ? (int)gridDim.x : kLLBlocks;
+  if ((int)blockIdx.x >= nb) return;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)nb * blockDim.x;
+  const uint8_t* mine = c.heap_local + a.src_off;
+  for (long long i = tid; i < (long long)valid * wpr; i += nthreads) {
+    const int g = (int)(i / wpr);
+    const int j = (int)(i - (long long)g * wpr);
+    int owner = 0;
+    while (owner + 1 < c.world && s_prefix[owner + 1] <= g) ++owner;
+    const uint4 pkt = ll_pack(ld_v2(mine + (uint64_t)g * a.row_bytes + (uint64_t)j * 8), flag);
+    st_v4(c.heap_peer[owner] + stage + (uint64_t)c.rank * per_src + ((uint64_t)(g - s_prefix[owner]) * wpr + j) * 16, pkt);
+  }
+  uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
+  for (long long i = tid; i < (long long)n * wpr; i += nthreads) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < c.world; ++s) {
+      const uint2 d = ll_wait(c, c.heap_local + stage + (uint64_t)s * per_src + (uint64_t)i * 16, flag, a.site);
+      acc[0] += bf16_lo(d.x); acc[1] += bf16_hi(d.x);
+      acc[2] += bf16_lo(d.y); acc[3] += bf16_hi(d.y);
+    }
+    st_v2(out + (uint64_t)i * 8, make_uint2(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3])));
+  }
+}
+
 template <bool EMU>
 __global__ void __launch_bounds__(512) rsv_kernel(const __grid_constant__ McbCtx ctx_p,
                                                    const __grid_constant__ McbRsvArgs args_p,
                                                    const McbCtx* ectx, const McbRsvArgs* eargs) {
   const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
   const McbRsvArgs& a = EMU ? eargs[blockIdx.y] : args_p;
-  pdl_wait();
   const int bid = blockIdx.x;
-  int n = *a.n_local;
-  const int offset = a.step_meta[1];
-  const int ep_max = a.step_meta[2];
+  int n = 0, valid_pre = 0, offset = 0, ep_max = 0;
+  if (a.meta_stable) {
+    n = *a.n_local;
+    valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2];
+  }
+  pdl_wait();
+  if (!a.meta_stable) {
+    n = *a.n_local;
+    valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2];
+  }
   const int nact = active_blocks((int)gridDim.x, ep_max, a.row_bytes, (int)blockDim.x);
   pdl_launch_dependents();
+  const bool bad = n < 0 || n > a.cap || offset < 0 || (long long)offset + n > (long long)a.cap * c.world;
+  if (a.ll_rows > 0 && c.world > 1) {
+    __shared__ int s_prefix[MCB_MAX_RANKS + 1];
+    const uint32_t flag = ll_next_flag(c, MCB_SITE_RSV_LL);
+    if (a.dtype == 0 && valid_pre > 0 && valid_pre <= a.ll_rows) {
+      const int valid = valid_pre;
+      if (bad || n > a.ll_src_rows) {
+        if (threadIdx.x == 0) report_error(c, MCB_ERR_BOUNDS, (uint32_t)a.site, (uint32_t)bid, (uint32_t)n, (uint32_t)valid);
+        return;
+      }
+      // Row ownership: prefix sums of the per-rank counts published by the metadata kernel.
+      if (threadIdx.x == 0) {
+        const uint32_t par = ((uint32_t)a.step_meta[3] - 1u) & 1u;
+        const uint8_t* counts = c.heap_local + a.counts_off + (uint64_t)par * MCB_MAX_RANKS * 4;
+        int run = 0;
+        for (int p = 0; p < c.world; ++p) {
+          s_prefix[p] = run;
+          run += (int)ld_relaxed_sys(counts + p * 4);
+        }
+        s_prefix[c.world] = run;
+      }
+      __syncthreads();
+      rsv_ll(c, a, n, offset, valid, flag, s_prefix);
+      return;
+    }
+    if (ep_max <= 0) return;
+  }
   if (bid >= nact) return;
   const uint32_t ep = *epoch_ptr(c, a.site, bid);
   if (n < 0) n = 0;
-  if (n > a.cap || offset < 0 || (long long)offset + n > (long long)a.cap * c.world) {
+  if (bad) {
     if (threadIdx.x == 0)
       report_error(c, n > a.cap ? MCB_ERR_CAPACITY : MCB_ERR_BOUNDS, (uint32_t)a.site, (uint32_t)bid,
                    (uint32_t)n, (uint32_t)offset);
@@ -349,9 +538,16 @@ int mcb_dense_decode_step(const McbCtx* ctx, const McbMetaArgs* meta, const McbA
                           const McbRsvArgs* rsv, int num_layers, int grid, int threads, int pdl,
                           cudaStream_t stream) {
   int err = mcb_launch_metadata(ctx, meta, pdl, stream);
+  // Only the first all-gather follows the kernel that writes the step metadata; every later
+  // launch may read the metadata before waiting on its predecessor.
+  McbAgvArgs agv_first = *agv, agv_rest = *agv;
+  McbRsvArgs rsv_all = *rsv;
+  agv_first.meta_stable = 0;
+  agv_rest.meta_stable = pdl ? 1 : 0;
+  rsv_all.meta_stable = pdl ? 1 : 0;
   for (int l = 0; l < num_layers && err == 0; ++l) {
-    err = mcb_launch_agv(ctx, agv, grid, threads, pdl, stream);
-    if (err == 0) err = mcb_launch_rsv(ctx, rsv, grid, threads, pdl, stream);
+    err = mcb_launch_agv(ctx, l == 0 ? &agv_first : &agv_rest, grid, threads, pdl, stream);
+    if (err == 0) err = mcb_launch_rsv(ctx, &rsv_all, grid, threads, pdl, stream);
   }
   return err;
 }

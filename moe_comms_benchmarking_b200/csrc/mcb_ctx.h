@@ -32,6 +32,8 @@
 #define MCB_SITE_FUSED_FC1 9
 #define MCB_SITE_FUSED_FC2 10
 #define MCB_SITE_LAYER 11
+#define MCB_SITE_AGV_LL 12       // launch counters of the low-latency paths (no flags used)
+#define MCB_SITE_RSV_LL 13
 #define MCB_SITE_TEST 15
 
 // Status codes written to status[0] (first error wins; 0 = healthy).
@@ -80,9 +82,18 @@ typedef struct {
   int32_t num_tensors;
   int32_t cap;                 // per-rank row capacity
   int32_t site;
-  int32_t reserved0;
+  // Non-zero when the kernel launched just before this one does not write n_local / step_meta
+  // (true for every launch of a step but the first after the metadata kernel): the kernel then
+  // reads them before waiting on its predecessor, hiding one memory round trip.
+  int32_t meta_stable;
   const int32_t* n_local;
   const int32_t* step_meta;
+  // Low-latency mode (0 rows = off): when the step holds at most ll_rows rows over all ranks,
+  // rows travel as 16-byte {data, flag, data, flag} packets through a staging area and the
+  // receiver polls the packets themselves, so no fence and no separate barrier are needed.
+  uint64_t ll_off;             // heap: [2][ll_rows][8-byte words per row] packets of 16 bytes
+  int32_t ll_rows;
+  int32_t reserved1;
 } McbAgvArgs;
 
 // Variable reduce-scatter: out[t,:] = sum over ranks of heap[src_off][(offset+t),:].
@@ -95,6 +106,14 @@ typedef struct {
   int32_t site;
   const int32_t* n_local;
   const int32_t* step_meta;
+  // Low-latency mode (bf16 only): every rank pushes its partial rows to their owner as
+  // flagged packets; the owner sums the world's packets in rank order in fp32.
+  uint64_t ll_off;             // heap: [2][world][ll_src_rows][row_bytes / 8] packets of 16 bytes
+  uint64_t counts_off;         // heap: int32 counts[2][MCB_MAX_RANKS] written by the metadata kernel
+  int32_t ll_rows;             // low-latency mode when the step holds at most this many rows in total
+  int32_t meta_stable;         // as in McbAgvArgs
+  int32_t ll_src_rows;         // rows per source region = min(cap, ll_rows)
+  int32_t reserved2;
 } McbRsvArgs;
 
 // All-to-all-V dispatch (one copy of a token per distinct destination rank).

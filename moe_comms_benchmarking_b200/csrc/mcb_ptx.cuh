@@ -47,6 +47,14 @@ __device__ __forceinline__ void st_b32(void* p, uint32_t v) {
   asm volatile("st.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
 }
 
+// Volatile 16-byte read used to poll flagged packets that a peer writes.
+__device__ __forceinline__ uint4 ld_v4_volatile(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 // ---- NVSwitch multicast ------------------------------------------------------------------
 // A store to a multicast address is replicated by the switch into every bound GPU.
 __device__ __forceinline__ void mm_st_v4(void* mc, uint4 v) {

@@ -25,6 +25,8 @@ SITE_A2A_DISPATCH, SITE_A2A_COMBINE = 3, 4
 SITE_UNIFORM_AG, SITE_UNIFORM_RS = 5, 6
 SITE_NORM_IN, SITE_NORM_OUT = 7, 8
 SITE_FUSED_FC1, SITE_FUSED_FC2, SITE_LAYER, SITE_TEST = 9, 10, 11, 15
+SITE_AGV_LL, SITE_RSV_LL = 12, 13
+LL_SITES = (SITE_AGV_LL, SITE_RSV_LL)
 
 ERR_NAMES = {0: "ok", 1: "timeout", 2: "capacity", 3: "bounds", 4: "routing"}
 
@@ -49,8 +51,9 @@ class McbMetaArgs(C.Structure):
 class McbAgvArgs(C.Structure):
     _fields_ = [
         ("src", _vp * MAX_TENSORS), ("dst_off", _u64 * MAX_TENSORS), ("row_bytes", _u32 * MAX_TENSORS),
-        ("num_tensors", _i32), ("cap", _i32), ("site", _i32), ("reserved0", _i32),
+        ("num_tensors", _i32), ("cap", _i32), ("site", _i32), ("meta_stable", _i32),
         ("n_local", _vp), ("step_meta", _vp),
+        ("ll_off", _u64), ("ll_rows", _i32), ("reserved1", _i32),
     ]
 
 
@@ -58,6 +61,8 @@ class McbRsvArgs(C.Structure):
     _fields_ = [
         ("out", _vp), ("src_off", _u64), ("row_bytes", _u32), ("dtype", _i32), ("cap", _i32),
         ("site", _i32), ("n_local", _vp), ("step_meta", _vp),
+        ("ll_off", _u64), ("counts_off", _u64), ("ll_rows", _i32), ("meta_stable", _i32),
+        ("ll_src_rows", _i32), ("reserved2", _i32),
     ]
 
 

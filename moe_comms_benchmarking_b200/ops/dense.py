@@ -48,6 +48,18 @@ def _check_grid(grid: int, threads: int):
         raise ValueError(f"threads {threads} must be a multiple of 32 in [32, 512]")
 
 
+def agv_ll_stage_bytes(ll_rows: int, row_bytes: list[int]) -> int:
+    """Staging bytes of the low-latency all-gather: 2 parities x ll_rows rows (all ranks together)
+    x one 16-byte packet per 8 bytes of row."""
+    return 2 * ll_rows * sum(rb // 8 for rb in row_bytes) * 16
+
+
+def rsv_ll_stage_bytes(world: int, ll_rows: int, cap: int, row_bytes: int) -> int:
+    """Staging bytes of the low-latency reduce-scatter: 2 parities x world sources x
+    min(cap, ll_rows) rows (one rank may own every row of a small step)."""
+    return 2 * world * min(cap, ll_rows) * (row_bytes // 8) * 16
+
+
 class MetadataPlan:
     """counts -> ``step_meta = [valid, offset, max, epoch]`` (int32, local device tensor)."""
 
@@ -76,7 +88,8 @@ class AllGatherVPlan:
     (16-byte rows use 128-bit accesses, 8-byte rows 64-bit)."""
 
     def __init__(self, heap: SymmetricHeap, dsts, srcs, n_local, step_meta, cap: int,
-                 site: int = _ext.SITE_AGV, grid: int = DEFAULT_GRID, threads: int = DEFAULT_THREADS):
+                 site: int = _ext.SITE_AGV, grid: int = DEFAULT_GRID, threads: int = DEFAULT_THREADS,
+                 ll_stage: HeapTensor | None = None, ll_rows: int = 0):
         if not (1 <= len(srcs) <= _ext.MAX_TENSORS) or len(srcs) != len(dsts):
             raise ValueError(f"need 1..{_ext.MAX_TENSORS} (dst, src) pairs")
         _check_grid(grid, threads)
@@ -102,6 +115,13 @@ class AllGatherVPlan:
             a.row_bytes[i] = rb
         a.num_tensors, a.cap, a.site = len(srcs), int(cap), int(site)
         a.n_local, a.step_meta = n_local.data_ptr(), step_meta.data_ptr()
+        if ll_stage is not None and ll_rows > 0:
+            need = agv_ll_stage_bytes(ll_rows, [_row_bytes(s) for s in srcs])
+            _check_heap_tensor(heap, ll_stage, "all_gather_v low-latency staging")
+            if ll_stage.nbytes < need:
+                raise ValueError(f"low-latency staging holds {ll_stage.nbytes} bytes, {need} needed")
+            a.ll_off, a.ll_rows = ll_stage.offset, int(ll_rows)
+            self._keep += (ll_stage,)
         self.args = a
 
     def launch(self, pdl: bool = False, stream=None):
@@ -115,7 +135,8 @@ class ReduceScatterVPlan:
     accumulated in fp32 (in the switch with multimem), fp32 operands in fp32."""
 
     def __init__(self, heap: SymmetricHeap, out: torch.Tensor, src: HeapTensor, n_local, step_meta, cap: int,
-                 site: int = _ext.SITE_RSV, grid: int = DEFAULT_GRID, threads: int = DEFAULT_THREADS):
+                 site: int = _ext.SITE_RSV, grid: int = DEFAULT_GRID, threads: int = DEFAULT_THREADS,
+                 ll_stage: HeapTensor | None = None, ll_rows: int = 0):
         _check_grid(grid, threads)
         rb = _row_bytes(out)
         _check_heap_tensor(heap, src, "reduce_scatter_v src")
@@ -134,6 +155,14 @@ class ReduceScatterVPlan:
         a.dtype = 1 if out.dtype == torch.float32 else 0
         a.cap, a.site = int(cap), int(site)
         a.n_local, a.step_meta = n_local.data_ptr(), step_meta.data_ptr()
+        if ll_stage is not None and ll_rows > 0 and out.dtype == torch.bfloat16:
+            need = rsv_ll_stage_bytes(heap.world, ll_rows, cap, rb)
+            _check_heap_tensor(heap, ll_stage, "reduce_scatter_v low-latency staging")
+            if ll_stage.nbytes < need:
+                raise ValueError(f"low-latency staging holds {ll_stage.nbytes} bytes, {need} needed")
+            a.ll_off, a.ll_rows, a.counts_off = ll_stage.offset, int(ll_rows), heap.counts_off
+            a.ll_src_rows = min(int(cap), int(ll_rows))
+            self._keep += (ll_stage,)
         self.args = a
 
     def launch(self, pdl: bool = False, stream=None):

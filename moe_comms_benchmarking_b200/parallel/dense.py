@@ -20,7 +20,7 @@ import torch.distributed as dist
 from ..config import Config
 from ..ops import _ext
 from ..ops.dense import (AllGatherVPlan, MetadataPlan, ReduceScatterVPlan, dense_decode_step, DEFAULT_GRID,
-                         DEFAULT_THREADS)
+                         DEFAULT_THREADS, agv_ll_stage_bytes, rsv_ll_stage_bytes)
 from .base import Dispatcher
 from .symm_heap import SymmetricHeap, required_bytes
 
@@ -30,7 +30,7 @@ class DenseDispatcher(Dispatcher):
 
     def __init__(self, cfg: Config, group, heap: SymmetricHeap | None = None, num_sms: int = DEFAULT_GRID,
                  threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto",
-                 combine_dtype=torch.bfloat16, device=None):
+                 combine_dtype=torch.bfloat16, ll_rows: int = 768, device=None):
         super().__init__(cfg, group, device)
         self.heap = heap
         self._own_heap = heap is None
@@ -39,25 +39,40 @@ class DenseDispatcher(Dispatcher):
         self.pdl = bool(pdl)
         self.transport = transport
         self.combine_dtype = combine_dtype
+        # Low-latency packet mode serves steps that hold at most ll_rows tokens over all ranks.
+        self.ll_rows = min(int(ll_rows), max(cfg.global_cap, 1)) if cfg.ep_size > 1 else 0
         self.kernel_launches_per_step = lambda nl: 1 + 2 * nl
 
     @staticmethod
-    def heap_specs(cfg: Config, combine_dtype=torch.bfloat16):
+    def _ll_bytes(cfg: Config, ll_rows: int):
+        H, K = cfg.hidden, cfg.topk
+        ll_rows = min(int(ll_rows), max(cfg.global_cap, 1)) if cfg.ep_size > 1 else 0
+        return (agv_ll_stage_bytes(ll_rows, [H * 2, K * 8, K * 4]),
+                rsv_ll_stage_bytes(cfg.ep_size, ll_rows, max(cfg.per_rank_cap, 1), H * 2))
+
+    @staticmethod
+    def heap_specs(cfg: Config, combine_dtype=torch.bfloat16, ll_rows: int = 768):
         g, H, K = max(cfg.global_cap, 1), cfg.hidden, cfg.topk
-        return [([g, H], torch.bfloat16), ([g, K], torch.int64), ([g, K], torch.float32), ([g, H], combine_dtype)]
+        a, r = DenseDispatcher._ll_bytes(cfg, ll_rows)
+        return [([g, H], torch.bfloat16), ([g, K], torch.int64), ([g, K], torch.float32), ([g, H], combine_dtype),
+                ([max(a, 16)], torch.uint8), ([max(r, 16)], torch.uint8)]
 
     def build(self):
         cfg, dev = self.cfg, self.device
         cap, g, H, K = max(cfg.per_rank_cap, 1), max(cfg.global_cap, 1), cfg.hidden, cfg.topk
         self.cap = cap
         if self.heap is None:
-            self.heap = SymmetricHeap(self.group, required_bytes(self.heap_specs(cfg, self.combine_dtype)), dev,
+            self.heap = SymmetricHeap(self.group,
+                                      required_bytes(self.heap_specs(cfg, self.combine_dtype, self.ll_rows)), dev,
                                       transport=self.transport)
         h = self.heap
         self.agv_h = h.alloc("ep_agv_h", [g, H], torch.bfloat16)
         self.agv_r = h.alloc("ep_agv_r", [g, K], torch.int64)
         self.agv_p = h.alloc("ep_agv_p", [g, K], torch.float32)
         self.rsv = h.alloc("ep_rsv", [g, H], self.combine_dtype)
+        a_bytes, r_bytes = self._ll_bytes(cfg, self.ll_rows)
+        self.ll_agv = h.alloc("ep_ll_agv", [max(a_bytes, 16)], torch.uint8)
+        self.ll_rsv = h.alloc("ep_ll_rsv", [max(r_bytes, 16)], torch.uint8)
         # Persistent local buffers (stable addresses for graph replay).
         self.in_hidden = torch.zeros(cap, H, dtype=torch.bfloat16, device=dev)
         self.in_routing = torch.zeros(cap, K, dtype=torch.int64, device=dev)
@@ -78,9 +93,11 @@ class DenseDispatcher(Dispatcher):
         self.meta_plan = MetadataPlan(h, self.n_local, self.step_metadata, self.cap)
         self.agv_plan = AllGatherVPlan(h, [self.agv_h, self.agv_r, self.agv_p],
                                        [self.in_hidden, self.in_routing, self.in_probs], self.n_local,
-                                       self.step_metadata, self.cap, grid=self.num_sms, threads=self.threads)
+                                       self.step_metadata, self.cap, grid=self.num_sms, threads=self.threads,
+                                       ll_stage=self.ll_agv, ll_rows=self.ll_rows)
         self.rsv_plan = ReduceScatterVPlan(h, self.out_buf, self.rsv, self.n_local, self.step_metadata, self.cap,
-                                           grid=self.num_sms, threads=self.threads)
+                                           grid=self.num_sms, threads=self.threads,
+                                           ll_stage=self.ll_rsv, ll_rows=self.ll_rows)
 
     def set_num_sms(self, num_sms: int):
         self.num_sms = int(num_sms)

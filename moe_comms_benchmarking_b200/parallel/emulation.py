@@ -84,7 +84,8 @@ class EmuWorld:
                                                    self.world, self._stream()), "emu metadata")
         torch.cuda.synchronize()
 
-    def all_gather_v(self, dsts, srcs, n_locals, step_metas, cap, grid=4, threads=256, site=_ext.SITE_AGV):
+    def all_gather_v(self, dsts, srcs, n_locals, step_metas, cap, grid=4, threads=256, site=_ext.SITE_AGV,
+                     ll_stage=None, ll_rows=0):
         """dsts: list over tensors of per-rank HeapTensor lists; srcs: list over tensors of per-rank tensors."""
         args = []
         for r in range(self.world):
@@ -94,13 +95,16 @@ class EmuWorld:
                 a.row_bytes[i] = srcs[i][r].shape[1] * srcs[i][r].element_size()
             a.num_tensors, a.cap, a.site = len(srcs), cap, site
             a.n_local, a.step_meta = n_locals[r].data_ptr(), step_metas[r].data_ptr()
+            if ll_stage is not None:
+                a.ll_off, a.ll_rows = ll_stage[r].offset, ll_rows
             args.append(a)
         d = self.upload(args)
         _ext.check(_ext.require().mcb_emu_agv(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
                                               self.world, grid, threads, self._stream()), "emu agv")
         torch.cuda.synchronize()
 
-    def reduce_scatter_v(self, outs, src, n_locals, step_metas, cap, grid=4, threads=256, site=_ext.SITE_RSV):
+    def reduce_scatter_v(self, outs, src, n_locals, step_metas, cap, grid=4, threads=256, site=_ext.SITE_RSV,
+                         ll_stage=None, ll_rows=0):
         args = []
         for r in range(self.world):
             a = _ext.McbRsvArgs()
@@ -109,6 +113,9 @@ class EmuWorld:
             a.dtype = 1 if outs[r].dtype == torch.float32 else 0
             a.cap, a.site = cap, site
             a.n_local, a.step_meta = n_locals[r].data_ptr(), step_metas[r].data_ptr()
+            if ll_stage is not None:
+                a.ll_off, a.ll_rows, a.counts_off = ll_stage[r].offset, ll_rows, self.counts_off
+                a.ll_src_rows = min(cap, ll_rows)
             args.append(a)
         d = self.upload(args)
         _ext.check(_ext.require().mcb_emu_rsv(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),

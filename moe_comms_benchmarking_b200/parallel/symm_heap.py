@@ -215,7 +215,12 @@ class SymmetricHeap:
         if self.world > 1:
             dist.barrier(self.group)
         self.buffer[:RESERVED_BYTES].zero_()
+        # The launch counters of the low-latency paths keep counting: their value is the flag
+        # carried by packets, and staging areas may still hold packets with earlier values.
+        keep = {s: self.epochs[s * _ext.MAX_BLOCKS:(s + 1) * _ext.MAX_BLOCKS].clone() for s in _ext.LL_SITES}
         self.epochs.zero_()
+        for s, v in keep.items():
+            self.epochs[s * _ext.MAX_BLOCKS:(s + 1) * _ext.MAX_BLOCKS] = v
         self.status.zero_()
         if self.device.type == "cuda":
             torch.cuda.synchronize()

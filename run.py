@@ -67,6 +67,9 @@ def parse_args(argv=None):
     p.add_argument("--expert", choices=["identity", "swiglu"], default="identity")
     p.add_argument("--dense-num-sms", type=int, default=148, help="CTA cap of the dense kernels")
     p.add_argument("--transport", choices=["auto", "multimem", "p2p"], default="auto")
+    p.add_argument("--ll-rows", type=int, default=768,
+                   help="dense dispatcher: steps with at most this many tokens over all ranks use "
+                        "low-latency flagged packets instead of barrier + multicast (0 = never)")
     p.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch")
     p.add_argument("--resume", action="store_true", help="keep rows already in --out and skip them")
     return p.parse_args(argv)
@@ -100,7 +103,7 @@ def build_dispatchers(names, cfg, group, args, device, sms_list):
         from moe_comms_benchmarking_b200.parallel.dense import DenseDispatcher
         specs = []
         if "dense" in names:
-            specs += DenseDispatcher.heap_specs(cfg)
+            specs += DenseDispatcher.heap_specs(cfg, ll_rows=args.ll_rows)
         if "a2a" in names:
             specs += A2ADispatcher.heap_specs(cfg, fp8)
         if "fused" in names:
@@ -111,7 +114,8 @@ def build_dispatchers(names, cfg, group, args, device, sms_list):
         if n == "a2a":
             out.append(A2ADispatcher(cfg, group, heap, num_sms=sms_list[0], pdl=not args.no_pdl, fp8_dispatch=fp8))
         elif n == "dense":
-            out.append(DenseDispatcher(cfg, group, heap, num_sms=args.dense_num_sms, pdl=not args.no_pdl))
+            out.append(DenseDispatcher(cfg, group, heap, num_sms=args.dense_num_sms, pdl=not args.no_pdl,
+                                       ll_rows=args.ll_rows))
         elif n == "fused":
             out.append(FusedExpertDispatcher(cfg, group, heap, pdl=not args.no_pdl))
         elif n == "nccl":

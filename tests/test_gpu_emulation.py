@@ -76,6 +76,48 @@ def test_all_gather_v_and_reduce_scatter_v(lib, grid, threads):
     w.check_status()
 
 
+@pytest.mark.parametrize("grid,threads", [(1, 128), (6, 512)])
+def test_low_latency_packet_mode(lib, grid, threads):
+    """Small steps travel as flagged packets (no barrier).  Steps alternate between packet mode
+    and the ordinary mode (more rows than the limit) on the same buffers."""
+    from moe_comms_benchmarking_b200.ops.dense import agv_ll_stage_bytes, rsv_ll_stage_bytes
+    W, cap, H, K, LL = 4, 16, 256, 22, 8
+    w = EmuWorld(W, 8 << 20, DEV)
+    g = torch.Generator(device=DEV).manual_seed(31)
+    dst_h = w.alloc([cap * W, H], torch.bfloat16)
+    dst_r = w.alloc([cap * W, K], torch.int64)
+    dst_p = w.alloc([cap * W, K], torch.float32)
+    rsv = w.alloc([cap * W, H], torch.bfloat16)
+    st_a = w.alloc([agv_ll_stage_bytes(LL, [H * 2, K * 8, K * 4])], torch.uint8)
+    st_r = w.alloc([rsv_ll_stage_bytes(W, LL, cap, H * 2)], torch.uint8)
+    metas = _metas(W)
+    for counts in ([4, 0, 2, 1], [1, 0, 0, 0], [3, 9, 1, 0], [2, 2, 2, 2], [0, 0, 0, 0], [0, 8, 0, 0], [4, 4, 4, 4]):
+        n_locals = _scalars(counts)
+        src_h = [torch.randn(cap, H, device=DEV, generator=g).to(torch.bfloat16) for _ in range(W)]
+        src_r = [torch.randint(0, 512, (cap, K), device=DEV, generator=g) for _ in range(W)]
+        src_p = [torch.rand(cap, K, device=DEV, generator=g) for _ in range(W)]
+        for d in (dst_h, dst_r, dst_p):
+            for r in range(W):
+                d[r].tensor.zero_()
+        w.metadata(n_locals, metas, cap)
+        w.all_gather_v([dst_h, dst_r, dst_p], [src_h, src_r, src_p], n_locals, metas, cap, grid, threads,
+                       ll_stage=st_a, ll_rows=LL)
+        valid = sum(counts)
+        full = [oracle.all_gather_v([s[r][:counts[r]] for r in range(W)]) for s in (src_h, src_r, src_p)]
+        for r in range(W):
+            assert torch.equal(dst_h[r].tensor[:valid], full[0])
+            assert torch.equal(dst_r[r].tensor[:valid], full[1])
+            assert torch.equal(dst_p[r].tensor[:valid], full[2])
+        for r in range(W):
+            rsv[r].tensor.copy_(torch.randn(cap * W, H, device=DEV, generator=g).to(torch.bfloat16))
+        outs = [torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV) for _ in range(W)]
+        w.reduce_scatter_v(outs, rsv, n_locals, metas, cap, grid, threads, ll_stage=st_r, ll_rows=LL)
+        want = oracle.reduce_scatter_v([rsv[r].tensor[:valid].cpu() for r in range(W)], counts)
+        for r in range(W):
+            assert torch.allclose(outs[r][:counts[r]].float().cpu(), want[r], rtol=2e-2, atol=2e-2)
+    w.check_status()
+
+
 def _a2a_case(W, E, K, H, counts, fp8, seed):
     cap = max(max(counts), 1)
     w = EmuWorld(W, 16 << 20, DEV)
