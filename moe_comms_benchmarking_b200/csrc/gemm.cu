@@ -1,0 +1,402 @@
+// Grouped expert GEMMs on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), sm_100a.
+//
+// The reference has no GEMM at all (its expert is the identity, bench_nvls.py:109-112); this
+// is the "real expert" half of the fused dispatcher.  One persistent kernel computes, for a
+// table of row tiles (expert, first pair row, row count), either
+//   MODE_FC1: act[row, i]  = silu(x[tok(row)] . Wg[e][i]) * (x[tok(row)] . Wu[e][i])
+//   MODE_FC2: y[row, h]    = prob[row] * (act[row] . Wd[e][h])
+// as D[128 rows, 256 cols] += A[128, K] * B[256, K]^T with one tcgen05.mma per 16 of K:
+//   * B (weights, K-major) is streamed by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle,
+//     no multicast) as two 128-row boxes per stage: gate rows + matching up rows for FC1, so
+//     that the SwiGLU needs no second pass; two consecutive row blocks for FC2;
+//   * A (token rows) is gathered by four producer warps straight from the gathered-token
+//     buffer through the pair -> token index list (this is the routing permute, fused into the
+//     operand load) and written to shared memory in the same 128-byte-swizzled K-major layout;
+//   * accumulators live in TMEM, double buffered (2 x 256 columns), so the epilogue of one
+//     tile overlaps the MMAs of the next; the epilogue reads them with tcgen05.ld;
+//   * one elected thread issues the MMAs; mbarriers (full/empty per stage, full/empty per
+//     accumulator) connect the roles; every wait is bounded and reports through a status word.
+// Rows of a tile beyond its row count are padding: their A rows are never written and their
+// accumulator rows never read (each output row depends on its own A row only).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "mcb_gemm.h"
+#include "mcb_launch.h"
+
+namespace mcb {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 64;          // 128 bytes of bf16: one swizzle atom row
+constexpr int kStages = 4;
+constexpr int kUmmaK = 16;
+constexpr int kABytes = kBlockM * kBlockK * 2;   // 16 KiB
+constexpr int kBBytes = kBlockN * kBlockK * 2;   // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTmemCols = 512;
+constexpr int kNumThreads = 320;                 // 10 warps
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+
+// ---- mbarrier / TMA / tcgen05 wrappers -------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+struct Abort {
+  volatile int* flag;        // shared: set once any wait of this CTA ran out
+  uint32_t* status;          // global status words (may be null)
+  uint64_t timeout_ns;
+};
+
+__device__ __forceinline__ uint64_t now_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false once this CTA has given up (now or earlier).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const Abort& ab, uint32_t where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = now_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*ab.flag) return false;
+    if (now_ns() - t0 > ab.timeout_ns) {
+      *ab.flag = 1;
+      if (ab.status && atomicCAS(ab.status, 0u, (uint32_t)MCB_GEMM_ERR_TIMEOUT) == 0u) {
+        ab.status[1] = where;
+        ab.status[2] = blockIdx.x;
+        ab.status[3] = parity;
+      }
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      :: "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(smem_dst)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate, M=128 N=256 K=16.
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :: "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 16 consecutive fp32 columns -> 16 registers per thread (thread = lane = row).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart (tile base 1024-byte aligned).
+__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address
+  d |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024u >> 4) << 32;                    // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                               // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: D=f32, A=B=bf16, both K-major, N=256, M=128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockN >> 3) << 17) |
+                                ((uint32_t)(kBlockM >> 4) << 24);
+
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kNumThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ McbGemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* full = bars;                       // [kStages]
+  uint64_t* empty = bars + kStages;            // [kStages]
+  uint64_t* tfull = bars + 2 * kStages;        // [2]
+  uint64_t* tempty = bars + 2 * kStages + 2;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1 + 4); mbar_init(&empty[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const Abort ab{abort_flag, a.status, a.timeout_ns};
+
+  const int n_tiles = a.n_total / (MODE == MCB_GEMM_FC1 ? 2 * 128 : kBlockN);  // FC1: n_total = 2I, 128 gate + 128 up per tile
+  const int num_m_tiles = *a.num_m_tiles;
+  const int total = num_m_tiles * n_tiles;
+  const int k_blocks = a.k_total / kBlockK;
+
+  if (warp == 0) {
+    // ---------------- TMA producer: weights ----------------
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        const int mt = tile / n_tiles, nt = tile - mt * n_tiles;
+        const int e = a.tile_expert[mt];
+        int r0, r1;
+        if (MODE == MCB_GEMM_FC1) {
+          r0 = e * a.n_total + nt * 128;               // gate rows
+          r1 = r0 + a.n_total / 2;                     // matching up rows
+        } else {
+          r0 = e * a.n_total + nt * kBlockN;
+          r1 = r0 + 128;
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&empty[s], ph ^ 1u, ab, 1))) break;
+          uint8_t* sb = smem + s * kStageBytes + kABytes;
+          mbar_arrive_expect_tx(&full[s], kBBytes);
+          tma_load_2d(sb, &w_map, &full[s], kb * kBlockK, r0);
+          tma_load_2d(sb + 128 * 128, &w_map, &full[s], kb * kBlockK, r1);
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      int acc = 0; uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+        if (!(ok = mbar_wait(&tempty[acc], acc_ph ^ 1u, ab, 2))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kBlockN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&full[s], ph, ab, 3))) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * kStageBytes);
+          const uint64_t da = make_sw128_desc(sa), db = make_sw128_desc(sa + kABytes);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            // 16 bf16 of K = 32 bytes further inside the swizzled row: +2 in 16-byte units
+            umma_bf16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), kInstrDesc, (kb | kk) != 0);
+          }
+          umma_commit(&empty[s]);             // stage may be refilled once these MMAs have read it
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);             // accumulator complete
+        if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------- epilogue: TMEM -> registers -> global ----------------
+    const int q = warp & 3;                  // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    int acc = 0; uint32_t acc_ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+      const int mt = tile / n_tiles, nt = tile - mt * n_tiles;
+      const int row0 = a.tile_row0[mt], rows = a.tile_rows[mt];
+      if (!(ok = mbar_wait(&tfull[acc], acc_ph, ab, 4))) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kBlockN);
+      const bool live = row_in_tile < rows;
+      const long long prow = (long long)row0 + row_in_tile;
+      if (MODE == MCB_GEMM_FC1) {
+        uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + prow * a.out_row_bytes + (long long)nt * 128 * 2;
+#pragma unroll 1
+        for (int j = 0; j < 8; ++j) {
+          uint32_t g[16], u[16];
+          tmem_ld16(t_row + j * 16, g);
+          tmem_ld16(t_row + 128 + j * 16, u);
+          tmem_ld_wait();
+          if (live) {
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float a0 = silu(__uint_as_float(g[2 * i])) * __uint_as_float(u[2 * i]);
+              const float a1 = silu(__uint_as_float(g[2 * i + 1])) * __uint_as_float(u[2 * i + 1]);
+              o[i] = pack2(a0, a1);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(orow + j * 32);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+        }
+      } else {
+        const float p = live ? (a.row_scale ? a.row_scale[prow] : 1.0f) : 0.f;
+        uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + prow * a.out_row_bytes + (long long)nt * kBlockN * 2;
+#pragma unroll 1
+        for (int j = 0; j < 16; ++j) {
+          uint32_t v[16];
+          tmem_ld16(t_row + j * 16, v);
+          tmem_ld_wait();
+          if (live) {
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = pack2(__uint_as_float(v[2 * i]) * p, __uint_as_float(v[2 * i + 1]) * p);
+            uint4* dst = reinterpret_cast<uint4*>(orow + j * 32);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+    }
+  } else {
+    // ---------------- A producers: gather token rows into swizzled shared memory ----------------
+    const int r = threadIdx.x - 6 * 32;      // row of the tile handled by this thread (0..127)
+    int s = 0; uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+      const int mt = tile / n_tiles;
+      const int row0 = a.tile_row0[mt], rows = a.tile_rows[mt];
+      const bool live = r < rows;
+      long long src_row = 0;
+      if (live) src_row = a.row_index ? (long long)a.row_index[row0 + r] : (long long)(row0 + r);
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(a.a_base) + src_row * a.a_row_bytes;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!(ok = mbar_wait(&empty[s], ph ^ 1u, ab, 5))) break;
+        if (live) {
+          uint8_t* sa = smem + s * kStageBytes + r * 128;
+          const uint4* g = reinterpret_cast<const uint4*>(src + (long long)kb * (kBlockK * 2));
+          uint4 v[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) v[c] = g[c];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sa + ((c ^ (r & 7)) << 4)) = v[c];
+        }
+        fence_proxy_async_smem();            // generic-proxy writes -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
+        if (++s == kStages) { s = 0; ph ^= 1u; }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) __nanosleep(50000);        // let any copy still in flight land before the CTA goes away
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace mcb
+
+using namespace mcb;
+
+extern "C" {
+
+int mcb_sizeof_gemm_args() { return (int)sizeof(McbGemmArgs); }
+int mcb_gemm_smem_bytes() { return kSmemBytes; }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Fills `out` (128 bytes, 64-byte aligned host memory) with a tensor map over a row-major bf16
+// matrix [rows, cols]: boxes of 128 rows x 64 columns, 128-byte swizzle.
+int mcb_make_weight_tmap(void* out, const void* base, uint64_t rows, uint64_t cols) {
+  static EncodeTiledFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (err != cudaSuccess) return (int)err;
+    if (qres != cudaDriverEntryPointSuccess || !fn) return (int)cudaErrorNotSupported;
+    encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  if (cols % kBlockK || rows % 128 || (reinterpret_cast<uintptr_t>(base) & 15)) return (int)cudaErrorInvalidValue;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBlockK, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                      dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+int mcb_launch_grouped_gemm(const void* tmap, const McbGemmArgs* args, int mode, int grid, int pdl, cudaStream_t stream) {
+  if (grid < 1 || !tmap || !args) return cudaErrorInvalidValue;
+  if (args->k_total % kBlockK || args->k_total < kBlockK) return cudaErrorInvalidValue;
+  if (mode == MCB_GEMM_FC1 ? (args->n_total % 256) : (args->n_total % kBlockN)) return cudaErrorInvalidValue;
+  if ((args->a_row_bytes & 15) || (args->out_row_bytes & 15)) return cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e1 = cudaFuncSetAttribute(grouped_gemm_kernel<MCB_GEMM_FC1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e2 = cudaFuncSetAttribute(grouped_gemm_kernel<MCB_GEMM_FC2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e1 != cudaSuccess) return (int)e1;
+    if (e2 != cudaSuccess) return (int)e2;
+    configured = true;
+  }
+  const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(tmap);
+  if (mode == MCB_GEMM_FC1)
+    return launch_kernel(grouped_gemm_kernel<MCB_GEMM_FC1>, dim3(grid), dim3(kNumThreads), kSmemBytes, stream, pdl, false, map, *args);
+  return launch_kernel(grouped_gemm_kernel<MCB_GEMM_FC2>, dim3(grid), dim3(kNumThreads), kSmemBytes, stream, pdl, false, map, *args);
+}
+
+}  // extern "C"

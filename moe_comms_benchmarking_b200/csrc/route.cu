@@ -1,0 +1,244 @@
+// Expert path glue for sm_100a: (1) routing of the gathered tokens to this rank's experts
+// (histogram -> offsets -> pair lists -> row-tile table for the grouped GEMMs), and (2) the
+// combine that sums each token's local expert outputs and reduce-scatters the partial sums
+// across ranks in the same kernel.
+//
+// The reference defers the permute "to the GEMM" and never performs it (its expert is the
+// identity; the only trace is the routing mask in bench_nvls.py:195).  Here the permute is an
+// index list: the FC1 kernel gathers token rows through pair_token[], so no token is copied.
+#include <cuda_runtime.h>
+
+#include "mcb_barrier.cuh"
+#include "mcb_gemm.h"
+#include "mcb_launch.h"
+
+namespace mcb {
+
+constexpr int kRouteThreads = 256;
+constexpr int kMaxLocalExperts = 1024;
+
+__device__ __forceinline__ bool spin_until_ge(const volatile int* p, int target, uint64_t timeout_ns) {
+  if (*p - target >= 0) return true;
+  uint64_t t0 = globaltimer_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (*p - target >= 0) return true;
+    if (globaltimer_ns() - t0 > timeout_ns) return false;
+  }
+}
+
+// One launch, two phases separated by a "last block computes the offsets" hand-over; blocks of
+// the same launch wait for it on a local counter, so the grid must be co-resident (<= #SMs).
+__global__ void __launch_bounds__(kRouteThreads) route_kernel(const __grid_constant__ McbRouteArgs a) {
+  __shared__ int s_hist[kMaxLocalExperts];
+  __shared__ int s_flag;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x;
+  const int E = a.num_local_experts;
+  int T = *a.num_tokens;
+  if (T < 0) T = 0;
+  if (T > a.max_tokens) T = a.max_tokens;
+  const int ready_base = *reinterpret_cast<volatile int*>(&a.sync[2]);   // stable until this launch's hand-over
+  const long long entries = (long long)T * a.topk;
+  const long long per_block = (entries + gridDim.x - 1) / gridDim.x;
+  const long long lo = per_block * blockIdx.x;
+  const long long hi = lo + per_block < entries ? lo + per_block : entries;
+
+  // ---- phase 1: histogram of the entries owned by this block ----
+  for (int e = tid; e < E; e += blockDim.x) s_hist[e] = 0;
+  __syncthreads();
+  for (long long i = lo + tid; i < hi; i += blockDim.x) {
+    const long long e = a.topk_idx[i] - a.expert_begin;
+    if (e >= 0 && e < E) atomicAdd(&s_hist[(int)e], 1);
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x)
+    if (s_hist[e]) atomicAdd(&a.expert_count[e], s_hist[e]);
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    s_flag = (atomicAdd(&a.sync[0], 1) == (int)gridDim.x - 1);
+    __threadfence();
+  }
+  __syncthreads();
+  if (s_flag) {
+    // Last block: exclusive prefix over experts, row-tile table, then release the others.
+    if (tid == 0) {
+      int run = 0, tiles = 0;
+      for (int e = 0; e < E; ++e) {
+        const int c = *reinterpret_cast<volatile int*>(&a.expert_count[e]);
+        a.expert_offset[e] = run;
+        for (int r0 = 0; r0 < c; r0 += 128) {
+          if (tiles < a.max_tiles) {
+            a.tile_expert[tiles] = e;
+            a.tile_row0[tiles] = run + r0;
+            a.tile_rows[tiles] = c - r0 < 128 ? c - r0 : 128;
+          }
+          ++tiles;
+        }
+        run += c;
+      }
+      a.expert_offset[E] = run;
+      if (tiles > a.max_tiles || run > a.max_pairs) {
+        if (a.status && atomicCAS(a.status, 0u, (uint32_t)MCB_ERR_CAPACITY) == 0u) {
+          a.status[1] = 100; a.status[2] = (uint32_t)tiles; a.status[3] = (uint32_t)run;
+        }
+        tiles = tiles > a.max_tiles ? a.max_tiles : tiles;
+      }
+      *a.num_m_tiles = tiles;
+      a.sync[0] = 0;
+      __threadfence();
+      atomicAdd(&a.sync[2], 1);
+    }
+  }
+  if (tid == 0) {
+    if (!spin_until_ge(reinterpret_cast<volatile int*>(&a.sync[2]), ready_base + 1, a.timeout_ns)) {
+      if (a.status && atomicCAS(a.status, 0u, (uint32_t)MCB_ERR_TIMEOUT) == 0u) { a.status[1] = 101; a.status[2] = blockIdx.x; }
+    }
+    __threadfence();
+  }
+  __syncthreads();
+
+  // ---- phase 2: place every local (token, k) entry into its expert's segment ----
+  for (long long i = lo + tid; i < hi; i += blockDim.x) {
+    const long long e = a.topk_idx[i] - a.expert_begin;
+    int pos = -1;
+    if (e >= 0 && e < E) {
+      pos = *reinterpret_cast<volatile int*>(&a.expert_offset[(int)e]) + atomicAdd(&a.expert_cursor[(int)e], 1);
+      if (pos < a.max_pairs) {
+        a.pair_token[pos] = (int)(i / a.topk);
+        a.pair_prob[pos] = a.topk_w ? a.topk_w[i] : 1.0f;
+      } else {
+        pos = -1;
+      }
+    }
+    a.pair_pos[i] = pos;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    s_flag = (atomicAdd(&a.sync[1], 1) == (int)gridDim.x - 1);
+  }
+  __syncthreads();
+  if (s_flag) {
+    // Last block out: scratch back to zero for the next launch.
+    for (int e = tid; e < E; e += blockDim.x) { a.expert_count[e] = 0; a.expert_cursor[e] = 0; }
+    if (tid == 0) a.sync[1] = 0;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Combine: block b owns the gathered tokens t with t % nact == b on EVERY rank.
+//   phase A  partial[t] = sum over the local (token, k) pairs of y[pair]       (this rank's heap)
+//   barrier  block b of every rank has written its tokens' partial sums
+//   phase B  for the tokens of block b that this rank owns: out = sum over ranks of partial[t]
+//            (multimem.ld_reduce in the switch, or peer loads).
+// ------------------------------------------------------------------------------------------------
+template <bool EMU>
+__global__ void __launch_bounds__(512) combine_kernel(const __grid_constant__ McbCtx ctx_p,
+                                                      const __grid_constant__ McbCombineArgs args_p,
+                                                      const McbCtx* ectx, const McbCombineArgs* eargs) {
+  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
+  const McbCombineArgs& a = EMU ? eargs[blockIdx.y] : args_p;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int T = a.step_meta[0], offset = a.step_meta[1];
+  int n = *a.n_local;
+  if (n < 0) n = 0;
+  if (n > a.cap) n = a.cap;
+  if (T <= 0) return;
+  int nact = (T + nwarps - 1) / nwarps;
+  if (nact > (int)gridDim.x) nact = (int)gridDim.x;
+  const int bid = blockIdx.x;
+  if (bid >= nact) return;
+  const uint32_t ep = *epoch_ptr(c, a.site, bid);
+  const int packs = a.hidden / 8;
+  const uint64_t row_bytes = (uint64_t)a.hidden * 2;
+  const uint8_t* y = reinterpret_cast<const uint8_t*>(a.y);
+  uint8_t* partial = c.heap_local + a.partial_off;
+
+  for (int t = bid + warp * nact; t < T; t += nact * nwarps) {
+    // pair rows of this token on this rank (lane k holds entry k)
+    for (int p0 = 0; p0 < packs; p0 += 32) {
+      const int p = p0 + lane;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int k = 0; k < a.topk; ++k) {
+        const int pos = a.pair_pos[(long long)t * a.topk + k];   // same address across the warp: broadcast
+        if (pos >= 0 && p < packs) {
+          const uint4 v = ld_v4(y + (uint64_t)pos * row_bytes + (uint64_t)p * 16);
+          acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x);
+          acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+          acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z);
+          acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+        }
+      }
+      if (p < packs)
+        st_v4(partial + (uint64_t)t * row_bytes + (uint64_t)p * 16,
+              make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                         pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7])));
+    }
+  }
+  block_barrier_all(c, a.site, bid, ep);
+
+  uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
+  for (int t = bid + warp * nact; t < T; t += nact * nwarps) {
+    if (t < offset || t >= offset + n) continue;
+    for (int p = lane; p < packs; p += 32) {
+      const uint64_t off = a.partial_off + (uint64_t)t * row_bytes + (uint64_t)p * 16;
+      uint4 v;
+      if (c.transport == MCB_TRANSPORT_MULTIMEM) {
+        v = mm_ld_reduce_bf16x8(c.heap_mc + off);
+      } else {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int k = 0; k < c.world; ++k) {
+          int q = c.rank + k;
+          if (q >= c.world) q -= c.world;
+          const uint4 w = ld_v4_stream(c.heap_peer[q] + off);
+          acc[0] += bf16_lo(w.x); acc[1] += bf16_hi(w.x);
+          acc[2] += bf16_lo(w.y); acc[3] += bf16_hi(w.y);
+          acc[4] += bf16_lo(w.z); acc[5] += bf16_hi(w.z);
+          acc[6] += bf16_lo(w.w); acc[7] += bf16_hi(w.w);
+        }
+        v = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+      }
+      st_v4(out + (uint64_t)(t - offset) * row_bytes + (uint64_t)p * 16, v);
+    }
+  }
+}
+
+}  // namespace mcb
+
+using namespace mcb;
+
+extern "C" {
+
+int mcb_sizeof_route_args() { return (int)sizeof(McbRouteArgs); }
+int mcb_sizeof_combine_args() { return (int)sizeof(McbCombineArgs); }
+
+int mcb_launch_route(const McbRouteArgs* args, int grid, int pdl, cudaStream_t stream) {
+  if (grid < 1 || grid > 128 || args->num_local_experts > kMaxLocalExperts || args->num_local_experts < 1)
+    return cudaErrorInvalidValue;
+  return launch_kernel(route_kernel, dim3(grid), dim3(kRouteThreads), 0, stream, pdl, false, *args);
+}
+
+int mcb_launch_combine(const McbCtx* ctx, const McbCombineArgs* args, int grid, int threads, int pdl,
+                       cudaStream_t stream) {
+  if (grid < 1 || grid > MCB_MAX_BLOCKS || threads < 32 || threads > 512 || (threads & 31) || args->hidden % 8)
+    return cudaErrorInvalidValue;
+  return launch_kernel(combine_kernel<false>, dim3(grid), dim3(threads), 0, stream, pdl, false, *ctx, *args,
+                       (const McbCtx*)nullptr, (const McbCombineArgs*)nullptr);
+}
+
+int mcb_emu_combine(const McbCtx* d_ctx, const McbCombineArgs* d_args, int world, int grid, int threads,
+                    cudaStream_t stream) {
+  if (grid < 1 || grid > MCB_MAX_BLOCKS || threads < 32 || threads > 512 || (threads & 31)) return cudaErrorInvalidValue;
+  McbCtx dummy{};
+  McbCombineArgs dargs{};
+  return launch_kernel(combine_kernel<true>, dim3(grid, world), dim3(threads), 0, stream, 0, true, dummy, dargs,
+                       d_ctx, d_args);
+}
+
+}  // extern "C"

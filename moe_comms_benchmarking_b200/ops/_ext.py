@@ -28,7 +28,7 @@ SITE_FUSED_FC1, SITE_FUSED_FC2, SITE_LAYER, SITE_TEST = 9, 10, 11, 15
 SITE_AGV_LL, SITE_RSV_LL = 12, 13
 LL_SITES = (SITE_AGV_LL, SITE_RSV_LL)
 
-ERR_NAMES = {0: "ok", 1: "timeout", 2: "capacity", 3: "bounds", 4: "routing"}
+ERR_NAMES = {0: "ok", 1: "timeout", 2: "capacity", 3: "bounds", 4: "routing", 5: "gemm-timeout"}
 
 _vp, _u64, _i32, _u32, _f32 = C.c_void_p, C.c_uint64, C.c_int32, C.c_uint32, C.c_float
 
@@ -87,9 +87,39 @@ class McbNormArgs(C.Structure):
                 ("tokens", _i32), ("reserved0", _i32)]
 
 
+class McbGemmArgs(C.Structure):
+    _fields_ = [
+        ("a_base", _vp), ("a_row_bytes", _u64), ("row_index", _vp), ("row_scale", _vp),
+        ("out", _vp), ("out_row_bytes", _u64),
+        ("tile_expert", _vp), ("tile_row0", _vp), ("tile_rows", _vp), ("num_m_tiles", _vp),
+        ("n_total", _i32), ("k_total", _i32), ("status", _vp), ("timeout_ns", _u64),
+    ]
+
+
+class McbRouteArgs(C.Structure):
+    _fields_ = [
+        ("topk_idx", _vp), ("topk_w", _vp), ("num_tokens", _vp),
+        ("topk", _i32), ("expert_begin", _i32), ("num_local_experts", _i32), ("max_tokens", _i32),
+        ("expert_count", _vp), ("expert_cursor", _vp), ("expert_offset", _vp),
+        ("pair_token", _vp), ("pair_prob", _vp), ("pair_pos", _vp),
+        ("tile_expert", _vp), ("tile_row0", _vp), ("tile_rows", _vp), ("num_m_tiles", _vp), ("sync", _vp),
+        ("max_pairs", _i32), ("max_tiles", _i32), ("status", _vp), ("timeout_ns", _u64),
+    ]
+
+
+class McbCombineArgs(C.Structure):
+    _fields_ = [
+        ("y", _vp), ("pair_pos", _vp), ("partial_off", _u64), ("out", _vp), ("n_local", _vp), ("step_meta", _vp),
+        ("hidden", _i32), ("topk", _i32), ("cap", _i32), ("site", _i32),
+    ]
+
+
+GEMM_FC1, GEMM_FC2 = 0, 1
+
 _STRUCTS = {
     "ctx": McbCtx, "meta_args": McbMetaArgs, "agv_args": McbAgvArgs, "rsv_args": McbRsvArgs,
     "a2a_dispatch_args": McbA2ADispatchArgs, "a2a_combine_args": McbA2ACombineArgs, "norm_args": McbNormArgs,
+    "gemm_args": McbGemmArgs, "route_args": McbRouteArgs, "combine_args": McbCombineArgs,
 }
 
 LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libmcb.so"

@@ -1,0 +1,163 @@
+"""Expert path: routing of gathered tokens, grouped SwiGLU GEMMs on tcgen05, and the combine
+that pre-sums a token's local expert outputs and reduce-scatters across ranks.
+
+The reference's expert is the identity (bench_nvls.py:109-112, bench_nccl.py:106-109); these
+plans are what turns the dense transport into a full expert-parallel MoE layer:
+
+    gathered tokens --RoutePlan--> pair lists, row tiles
+                    --GroupedGemmPlan(FC1)--> act = silu(x Wg^T) * (x Wu^T)      (token gather fused)
+                    --GroupedGemmPlan(FC2)--> y = prob * (act Wd^T)
+                    --ExpertCombinePlan--> out[t] = sum over ranks and local pairs of y
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _ext
+from .dense import _check_heap_tensor
+from ..parallel.symm_heap import HeapTensor, SymmetricHeap
+
+NUM_SMS = 148
+BLOCK_M = 128
+
+
+class ExpertWeights:
+    """bf16 weights of this rank's experts: ``w_gate_up [E_loc, 2*I, H]`` (gate rows, then up
+    rows) and ``w_down [E_loc, H, I]``, plus their TMA tensor maps."""
+
+    def __init__(self, num_local_experts: int, hidden: int, intermediate: int, device, seed: int = 0, std: float = 0.02):
+        if hidden % 256 or intermediate % 128:
+            raise ValueError("hidden must be a multiple of 256 and intermediate a multiple of 128")
+        g = torch.Generator(device=device).manual_seed(seed)
+        self.num_local_experts, self.hidden, self.intermediate = num_local_experts, hidden, intermediate
+        self.w_gate_up = (torch.randn(num_local_experts, 2 * intermediate, hidden, device=device, generator=g,
+                                      dtype=torch.float32) * std).to(torch.bfloat16)
+        self.w_down = (torch.randn(num_local_experts, hidden, intermediate, device=device, generator=g,
+                                   dtype=torch.float32) * std).to(torch.bfloat16)
+        self.map_gate_up = make_weight_tmap(self.w_gate_up.view(-1, hidden))
+        self.map_down = make_weight_tmap(self.w_down.view(-1, intermediate))
+
+    def bytes(self) -> int:
+        return (self.w_gate_up.numel() + self.w_down.numel()) * 2
+
+
+def make_weight_tmap(w2d: torch.Tensor):
+    """128-byte tensor map (kept in 64-byte aligned host memory) over a row-major bf16 matrix."""
+    if w2d.dtype != torch.bfloat16 or w2d.dim() != 2 or not w2d.is_contiguous():
+        raise ValueError("weights must be a contiguous 2-D bf16 tensor")
+    raw = (C.c_uint8 * 192)()
+    addr = (C.addressof(raw) + 63) & ~63
+    lib = _ext.require()
+    _ext.check(lib.mcb_make_weight_tmap(C.c_void_p(addr), C.c_void_p(w2d.data_ptr()), C.c_uint64(w2d.shape[0]),
+                                        C.c_uint64(w2d.shape[1])), "make_weight_tmap")
+    return (raw, addr)     # keep `raw` alive; `addr` is what launches take
+
+
+class RouteBuffers:
+    """Device buffers written by the routing kernel and read by the GEMMs and the combine."""
+
+    def __init__(self, max_tokens: int, topk: int, num_local_experts: int, device):
+        self.max_tokens, self.topk, self.E = max_tokens, topk, num_local_experts
+        self.max_pairs = max_tokens * min(topk, num_local_experts)
+        self.max_tiles = num_local_experts + self.max_pairs // BLOCK_M + 1
+        i32 = dict(dtype=torch.int32, device=device)
+        self.expert_count = torch.zeros(num_local_experts, **i32)
+        self.expert_cursor = torch.zeros(num_local_experts, **i32)
+        self.expert_offset = torch.zeros(num_local_experts + 1, **i32)
+        self.pair_token = torch.zeros(max(self.max_pairs, 1), **i32)
+        self.pair_prob = torch.zeros(max(self.max_pairs, 1), dtype=torch.float32, device=device)
+        self.pair_pos = torch.full((max_tokens, topk), -1, **i32)
+        self.tile_expert = torch.zeros(self.max_tiles, **i32)
+        self.tile_row0 = torch.zeros(self.max_tiles, **i32)
+        self.tile_rows = torch.zeros(self.max_tiles, **i32)
+        self.num_m_tiles = torch.zeros(1, **i32)
+        self.sync = torch.zeros(4, **i32)
+
+
+class RoutePlan:
+    def __init__(self, bufs: RouteBuffers, topk_idx: torch.Tensor, topk_w: torch.Tensor | None, num_tokens: torch.Tensor,
+                 expert_begin: int, status: torch.Tensor | None = None, grid: int = 32, timeout_s: float = 2.0):
+        if topk_idx.dtype != torch.int64 or topk_idx.dim() != 2 or topk_idx.shape[1] != bufs.topk:
+            raise ValueError("topk_idx must be int64 [tokens, topk]")
+        if topk_idx.shape[0] < bufs.max_tokens:
+            raise ValueError("topk_idx holds fewer rows than max_tokens")
+        if num_tokens.dtype != torch.int32:
+            raise ValueError("num_tokens must be an int32 device scalar")
+        if not (1 <= grid <= 128):
+            raise ValueError("routing grid must be in [1, 128] (its blocks wait on one another)")
+        self.bufs, self.grid = bufs, grid
+        self._keep = (topk_idx, topk_w, num_tokens, status)
+        a = _ext.McbRouteArgs()
+        a.topk_idx, a.topk_w, a.num_tokens = topk_idx.data_ptr(), _ext.ptr(topk_w), num_tokens.data_ptr()
+        a.topk, a.expert_begin, a.num_local_experts, a.max_tokens = bufs.topk, int(expert_begin), bufs.E, bufs.max_tokens
+        for f in ("expert_count", "expert_cursor", "expert_offset", "pair_token", "pair_prob", "pair_pos",
+                  "tile_expert", "tile_row0", "tile_rows", "num_m_tiles", "sync"):
+            setattr(a, f, getattr(bufs, f).data_ptr())
+        a.max_pairs, a.max_tiles = bufs.max_pairs, bufs.max_tiles
+        a.status, a.timeout_ns = _ext.ptr(status), int(timeout_s * 1e9)
+        self.args = a
+
+    def launch(self, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        _ext.check(lib.mcb_launch_route(C.byref(self.args), self.grid, int(pdl), _ext.stream_handle(stream)), "route")
+
+
+class GroupedGemmPlan:
+    """One grouped GEMM over the row tiles of ``route``.  ``mode`` FC1: ``a`` = gathered hidden
+    ``[T, H]`` gathered through ``pair_token``, ``out`` = act ``[P, I]``.  FC2: ``a`` = act
+    (identity rows), ``out`` = y ``[P, H]`` scaled by ``pair_prob``."""
+
+    def __init__(self, mode: int, tmap, route: RouteBuffers, a: torch.Tensor, out: torch.Tensor, n_total: int,
+                 k_total: int, status: torch.Tensor | None = None, grid: int = NUM_SMS, timeout_s: float = 2.0):
+        if a.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or not a.is_contiguous() or not out.is_contiguous():
+            raise ValueError("A and out must be contiguous bf16")
+        if a.shape[-1] != k_total:
+            raise ValueError(f"A rows hold {a.shape[-1]} values, k_total is {k_total}")
+        n_out = n_total // 2 if mode == _ext.GEMM_FC1 else n_total
+        if out.shape[-1] != n_out or out.shape[0] < route.max_pairs:
+            raise ValueError("out must be [max_pairs, n_out]")
+        if k_total % 64 or n_total % 256:
+            raise ValueError("k_total must be a multiple of 64 and n_total of 256")
+        self.mode, self.tmap, self.grid = mode, tmap, grid
+        self._keep = (route, a, out, status)
+        g = _ext.McbGemmArgs()
+        g.a_base, g.a_row_bytes = a.data_ptr(), k_total * 2
+        g.row_index = route.pair_token.data_ptr() if mode == _ext.GEMM_FC1 else 0
+        g.row_scale = route.pair_prob.data_ptr() if mode == _ext.GEMM_FC2 else 0
+        g.out, g.out_row_bytes = out.data_ptr(), n_out * 2
+        g.tile_expert, g.tile_row0 = route.tile_expert.data_ptr(), route.tile_row0.data_ptr()
+        g.tile_rows, g.num_m_tiles = route.tile_rows.data_ptr(), route.num_m_tiles.data_ptr()
+        g.n_total, g.k_total = int(n_total), int(k_total)
+        g.status, g.timeout_ns = _ext.ptr(status), int(timeout_s * 1e9)
+        self.args = g
+
+    def launch(self, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        _ext.check(lib.mcb_launch_grouped_gemm(C.c_void_p(self.tmap[1]), C.byref(self.args), self.mode, self.grid,
+                                               int(pdl), _ext.stream_handle(stream)), "grouped_gemm")
+
+
+class ExpertCombinePlan:
+    def __init__(self, heap: SymmetricHeap, y: torch.Tensor, route: RouteBuffers, partial: HeapTensor, out: torch.Tensor,
+                 n_local: torch.Tensor, step_meta: torch.Tensor, cap: int, grid: int = NUM_SMS, threads: int = 512,
+                 site: int = _ext.SITE_FUSED_FC2):
+        hidden = y.shape[-1]
+        if y.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or hidden % 8:
+            raise ValueError("y and out must be bf16 with hidden a multiple of 8")
+        _check_heap_tensor(heap, partial, "combine partial sums")
+        if partial.nbytes < cap * heap.world * hidden * 2:
+            raise ValueError("partial-sum buffer smaller than [cap * world, hidden]")
+        self.heap, self.grid, self.threads = heap, grid, threads
+        self._keep = (y, route, partial, out, n_local, step_meta)
+        a = _ext.McbCombineArgs()
+        a.y, a.pair_pos, a.partial_off, a.out = y.data_ptr(), route.pair_pos.data_ptr(), partial.offset, out.data_ptr()
+        a.n_local, a.step_meta = n_local.data_ptr(), step_meta.data_ptr()
+        a.hidden, a.topk, a.cap, a.site = hidden, route.topk, int(cap), int(site)
+        self.args = a
+
+    def launch(self, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        _ext.check(lib.mcb_launch_combine(C.byref(self.heap.ctx()), C.byref(self.args), self.grid, self.threads,
+                                          int(pdl), _ext.stream_handle(stream)), "expert_combine")
