@@ -11,7 +11,9 @@
 //     that the SwiGLU needs no second pass; two consecutive row blocks for FC2;
 //   * A (token rows) is gathered by four producer warps straight from the gathered-token
 //     buffer through the pair -> token index list (this is the routing permute, fused into the
-//     operand load) and written to shared memory in the same 128-byte-swizzled K-major layout;
+//     operand load): each thread owns one row and issues asynchronous 16-byte copies
+//     (cp.async) into the same 128-byte-swizzled K-major layout, completion arriving on the
+//     stage's mbarrier, so the gather runs as many stages ahead as the weight stream does;
 //   * accumulators live in TMEM, double buffered (2 x 256 columns), so the epilogue of one
 //     tile overlaps the MMAs of the next; the epilogue reads them with tcgen05.ld;
 //   * one elected thread issues the MMAs; mbarriers (full/empty per stage, full/empty per
@@ -101,6 +103,15 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       :: "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
 
+// Asynchronous 16-byte global -> shared copy (L2 only), and "arrive on this mbarrier once all
+// my earlier cp.async copies have landed" (counts as one of the barrier's expected arrivals).
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -174,7 +185,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1 + 4); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1 + 128); mbar_init(&empty[s], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -229,6 +240,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kBlockN);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!(ok = mbar_wait(&full[s], ph, ab, 3))) break;
+          fence_proxy_async_smem();           // the A rows were written by cp.async, not by TMA
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * kStageBytes);
           const uint64_t da = make_sw128_desc(sa), db = make_sw128_desc(sa + kABytes);
@@ -319,16 +331,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         if (!(ok = mbar_wait(&empty[s], ph ^ 1u, ab, 5))) break;
         if (live) {
           uint8_t* sa = smem + s * kStageBytes + r * 128;
-          const uint4* g = reinterpret_cast<const uint4*>(src + (long long)kb * (kBlockK * 2));
-          uint4 v[8];
+          const uint8_t* g = src + (long long)kb * (kBlockK * 2);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) v[c] = g[c];
-#pragma unroll
-          for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sa + ((c ^ (r & 7)) << 4)) = v[c];
+          for (int c = 0; c < 8; ++c) cp_async_16(sa + ((c ^ (r & 7)) << 4), g + c * 16);
         }
-        fence_proxy_async_smem();            // generic-proxy writes -> visible to the tensor core
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full[s]);
+        cp_async_arrive_noinc(&full[s]);     // arrives when this thread's copies have landed
         if (++s == kStages) { s = 0; ph ^= 1u; }
       }
     }

@@ -16,6 +16,7 @@ namespace mcb {
 
 constexpr int kRouteThreads = 256;
 constexpr int kMaxLocalExperts = 1024;
+constexpr int kSingleBlockEntries = 16384;   // (token, k) entries one block routes alone
 
 __device__ __forceinline__ bool spin_until_ge(const volatile int* p, int target, uint64_t timeout_ns) {
   if (*p - target >= 0) return true;
@@ -41,6 +42,54 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const __grid_const
   if (T > a.max_tokens) T = a.max_tokens;
   const int ready_base = *reinterpret_cast<volatile int*>(&a.sync[2]);   // stable until this launch's hand-over
   const long long entries = (long long)T * a.topk;
+  if (entries <= kSingleBlockEntries) {
+    // Small step: block 0 does everything in shared memory (no hand-over between blocks, no
+    // global atomics), the other blocks leave at once.
+    if (blockIdx.x != 0) return;
+    __shared__ int s_cursor[kMaxLocalExperts];
+    for (int e = tid; e < E; e += blockDim.x) { s_hist[e] = 0; s_cursor[e] = 0; }
+    __syncthreads();
+    for (int i = tid; i < (int)entries; i += blockDim.x) {
+      const long long e = a.topk_idx[i] - a.expert_begin;
+      if (e >= 0 && e < E) atomicAdd(&s_hist[(int)e], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int run = 0, tiles = 0;
+      for (int e = 0; e < E; ++e) {
+        const int c = s_hist[e];
+        s_hist[e] = run;
+        a.expert_offset[e] = run;
+        for (int r0 = 0; r0 < c; r0 += 128) {
+          if (tiles < a.max_tiles) {
+            a.tile_expert[tiles] = e;
+            a.tile_row0[tiles] = run + r0;
+            a.tile_rows[tiles] = c - r0 < 128 ? c - r0 : 128;
+          }
+          ++tiles;
+        }
+        run += c;
+      }
+      a.expert_offset[E] = run;
+      *a.num_m_tiles = tiles < a.max_tiles ? tiles : a.max_tiles;
+    }
+    __syncthreads();
+    for (int i = tid; i < (int)entries; i += blockDim.x) {
+      const long long e = a.topk_idx[i] - a.expert_begin;
+      int pos = -1;
+      if (e >= 0 && e < E) {
+        pos = s_hist[(int)e] + atomicAdd(&s_cursor[(int)e], 1);
+        if (pos < a.max_pairs) {
+          a.pair_token[pos] = i / a.topk;
+          a.pair_prob[pos] = a.topk_w ? a.topk_w[i] : 1.0f;
+        } else {
+          pos = -1;
+        }
+      }
+      a.pair_pos[i] = pos;
+    }
+    return;
+  }
   const long long per_block = (entries + gridDim.x - 1) / gridDim.x;
   const long long lo = per_block * blockIdx.x;
   const long long hi = lo + per_block < entries ? lo + per_block : entries;
@@ -64,10 +113,12 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const __grid_const
   __syncthreads();
   if (s_flag) {
     // Last block: exclusive prefix over experts, row-tile table, then release the others.
+    for (int e = tid; e < E; e += blockDim.x) s_hist[e] = *reinterpret_cast<volatile int*>(&a.expert_count[e]);
+    __syncthreads();
     if (tid == 0) {
       int run = 0, tiles = 0;
       for (int e = 0; e < E; ++e) {
-        const int c = *reinterpret_cast<volatile int*>(&a.expert_count[e]);
+        const int c = s_hist[e];
         a.expert_offset[e] = run;
         for (int r0 = 0; r0 < c; r0 += 128) {
           if (tiles < a.max_tiles) {
@@ -101,11 +152,13 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const __grid_const
   __syncthreads();
 
   // ---- phase 2: place every local (token, k) entry into its expert's segment ----
+  for (int e = tid; e < E; e += blockDim.x) s_hist[e] = *reinterpret_cast<volatile int*>(&a.expert_offset[e]);
+  __syncthreads();
   for (long long i = lo + tid; i < hi; i += blockDim.x) {
     const long long e = a.topk_idx[i] - a.expert_begin;
     int pos = -1;
     if (e >= 0 && e < E) {
-      pos = *reinterpret_cast<volatile int*>(&a.expert_offset[(int)e]) + atomicAdd(&a.expert_cursor[(int)e], 1);
+      pos = s_hist[(int)e] + atomicAdd(&a.expert_cursor[(int)e], 1);
       if (pos < a.max_pairs) {
         a.pair_token[pos] = (int)(i / a.topk);
         a.pair_prob[pos] = a.topk_w ? a.topk_w[i] : 1.0f;
@@ -149,8 +202,9 @@ __global__ void __launch_bounds__(512) combine_kernel(const __grid_constant__ Mc
   if (n < 0) n = 0;
   if (n > a.cap) n = a.cap;
   if (T <= 0) return;
-  int nact = (T + nwarps - 1) / nwarps;
-  if (nact > (int)gridDim.x) nact = (int)gridDim.x;
+  // One token per block while there are fewer tokens than blocks (shortest critical path), the
+  // whole grid otherwise; identical on every rank.
+  int nact = T < (int)gridDim.x ? T : (int)gridDim.x;
   const int bid = blockIdx.x;
   if (bid >= nact) return;
   const uint32_t ep = *epoch_ptr(c, a.site, bid);
@@ -160,24 +214,46 @@ __global__ void __launch_bounds__(512) combine_kernel(const __grid_constant__ Mc
   uint8_t* partial = c.heap_local + a.partial_off;
 
   for (int t = bid + warp * nact; t < T; t += nact * nwarps) {
-    // pair rows of this token on this rank (lane k holds entry k)
-    for (int p0 = 0; p0 < packs; p0 += 32) {
-      const int p = p0 + lane;
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int k = 0; k < a.topk; ++k) {
-        const int pos = a.pair_pos[(long long)t * a.topk + k];   // same address across the warp: broadcast
-        if (pos >= 0 && p < packs) {
-          const uint4 v = ld_v4(y + (uint64_t)pos * row_bytes + (uint64_t)p * 16);
-          acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x);
-          acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
-          acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z);
-          acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+    // Pair rows of this token on this rank: lanes read the token's routing slots in parallel,
+    // then the warp walks only the local ones.
+    for (int p0 = 0; p0 < packs; p0 += 128) {
+      float acc[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
+      for (int k0 = 0; k0 < a.topk; k0 += 32) {
+        const int k = k0 + lane;
+        const int my_pos = k < a.topk ? a.pair_pos[(long long)t * a.topk + k] : -1;
+        uint32_t have = __ballot_sync(0xffffffffu, my_pos >= 0);
+        while (have) {
+          const int src_lane = __ffs(have) - 1;
+          have &= have - 1;
+          const int pos = __shfl_sync(0xffffffffu, my_pos, src_lane);
+          const uint8_t* row = y + (uint64_t)pos * row_bytes;
+          uint4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int p = p0 + u * 32 + lane;
+            v[u] = p < packs ? ld_v4(row + (uint64_t)p * 16) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            acc[u][0] += bf16_lo(v[u].x); acc[u][1] += bf16_hi(v[u].x);
+            acc[u][2] += bf16_lo(v[u].y); acc[u][3] += bf16_hi(v[u].y);
+            acc[u][4] += bf16_lo(v[u].z); acc[u][5] += bf16_hi(v[u].z);
+            acc[u][6] += bf16_lo(v[u].w); acc[u][7] += bf16_hi(v[u].w);
+          }
         }
       }
-      if (p < packs)
-        st_v4(partial + (uint64_t)t * row_bytes + (uint64_t)p * 16,
-              make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
-                         pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7])));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int p = p0 + u * 32 + lane;
+        if (p < packs)
+          st_v4(partial + (uint64_t)t * row_bytes + (uint64_t)p * 16,
+                make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]),
+                           pack_bf16x2(acc[u][4], acc[u][5]), pack_bf16x2(acc[u][6], acc[u][7])));
+      }
     }
   }
   block_barrier_all(c, a.site, bid, ep);
