@@ -81,8 +81,13 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
   const int row_packs = a.hidden / 8;  // 16-byte packs of bf16 per row
   const uint8_t* x = reinterpret_cast<const uint8_t*>(a.x);
   DestList& L = s_list[warp];
+  // Only as many blocks as there are warps' worth of tokens take part (at least one, which
+  // also publishes the counts of a rank without tokens); the others leave at once.
+  int nwork = (n + nwarps - 1) / nwarps;
+  nwork = nwork < 1 ? 1 : (nwork > (int)gridDim.x ? (int)gridDim.x : nwork);
+  if ((int)blockIdx.x >= nwork) return;
 
-  for (int t = blockIdx.x * nwarps + warp; t < n; t += gridDim.x * nwarps) {
+  for (int t = blockIdx.x * nwarps + warp; t < n; t += nwork * nwarps) {
     // Destination ranks of this token as a bitmask (3 words cover MCB_MAX_RANKS = 72).
     uint32_t m0 = 0, m1 = 0, m2 = 0;
     for (int k = lane; k < a.topk; k += 32) {
@@ -179,10 +184,14 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
   // Grid-wide completion: the last block publishes counts and meets the other ranks.
   __syncthreads();
   if (tid == 0) {
-    fence_sys();
-    const int prev = atomicAdd(&a.send_count[MCB_MAX_RANKS], 1);
-    fence_sys();
-    s_last = (prev == (int)gridDim.x - 1);
+    if (nwork > 1) {
+      fence_sys();                      // this block's peer stores are performed before it counts itself done
+      const int prev = atomicAdd(&a.send_count[MCB_MAX_RANKS], 1);
+      __threadfence();                  // the other blocks are on this GPU: device scope is enough here
+      s_last = (prev == nwork - 1);
+    } else {
+      s_last = 1;                       // single block: the release on the flag below covers its stores
+    }
   }
   __syncthreads();
   if (!s_last) return;
@@ -210,16 +219,35 @@ __global__ void __launch_bounds__(512) a2a_combine_kernel(const __grid_constant_
   int n = *a.n_local;
   if (n < 0) n = 0;
   if (n > a.cap) n = a.cap;
-  const uint32_t ep = *epoch_ptr(c, MCB_SITE_A2A_COMBINE, blockIdx.x);
-  // Leading barrier: every destination's expert outputs were written by kernels that
-  // finished before its block arrived here (no release fence needed).
-  block_barrier_all<false>(c, MCB_SITE_A2A_COMBINE, blockIdx.x, ep);
+  const uint32_t launch = next_launch_count(c, MCB_SITE_A2A_COMBINE);
+  int nwork = (n + nwarps - 1) / nwarps;
+  nwork = nwork < 1 ? 1 : (nwork > (int)gridDim.x ? (int)gridDim.x : nwork);
+  if ((int)blockIdx.x >= nwork) return;
+  if (W > 1) {
+    // Leading barrier: every destination's expert outputs were written by kernels that finished
+    // before it arrived here, so the arrival needs no release fence.  Block 0 alone meets the
+    // other ranks (one flag slot) and then releases this rank's other working blocks through a
+    // local word; blocks without tokens have left already.
+    uint32_t* go = epoch_ptr(c, MCB_SITE_A2A_GO, 0);
+    if (blockIdx.x == 0) {
+      signal_all<false>(c, MCB_SITE_A2A_COMBINE, 0);
+      if (tid == 0) {
+        wait_flag(c, MCB_SITE_A2A_COMBINE, 0, launch * (uint32_t)W);
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(go) = launch;
+      }
+    } else if (tid == 0) {
+      wait_local(c, go, launch, MCB_SITE_A2A_COMBINE);
+      __threadfence();
+    }
+    __syncthreads();
+  }
 
   const int row_packs = a.hidden / 8;
   const uint64_t row_bytes = (uint64_t)a.hidden * 2;
   uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
   DestList& L = s_list[warp];
-  for (int t = blockIdx.x * nwarps + warp; t < n; t += gridDim.x * nwarps) {
+  for (int t = blockIdx.x * nwarps + warp; t < n; t += nwork * nwarps) {
     int m = 0;
     for (int d0 = 0; d0 < W; d0 += 32) {
       const int d = d0 + lane;

@@ -179,15 +179,7 @@ __device__ __forceinline__ uint2 ll_wait(const McbCtx& c, const uint8_t* slot, u
   }
 }
 
-// Every block of every launch advances its own launch counter, whether it has work or not, so
-// the counters (and with them flag and parity) agree across blocks and ranks.
-__device__ __forceinline__ uint32_t ll_next_flag(const McbCtx& c, int site) {
-  uint32_t* ctr = epoch_ptr(c, site, blockIdx.x);
-  const uint32_t v = *ctr + 1u;
-  __syncthreads();
-  if (threadIdx.x == 0) *ctr = v;
-  return v;
-}
+__device__ __forceinline__ uint32_t ll_next_flag(const McbCtx& c, int site) { return next_launch_count(c, site); }
 
 __device__ __forceinline__ bool agv_ll_eligible(const McbCtx& c, const McbAgvArgs& a, int valid) {
   if (c.world == 1 || a.ll_rows <= 0 || valid <= 0 || valid > a.ll_rows) return false;

@@ -91,4 +91,32 @@ __device__ __forceinline__ void block_barrier_all(const McbCtx& c, int site, int
   __syncthreads();
 }
 
+// Per-block launch counter: every block of every launch advances its own counter, whether it
+// has work or not, so the value is the same in all blocks and on all ranks.  Call from all
+// threads of the block; returns the number of this launch (1, 2, ...).
+__device__ __forceinline__ uint32_t next_launch_count(const McbCtx& c, int site) {
+  uint32_t* ctr = epoch_ptr(c, site, blockIdx.x);
+  const uint32_t v = *ctr + 1u;
+  __syncthreads();
+  if (threadIdx.x == 0) *ctr = v;
+  return v;
+}
+
+// Bounded spin on a LOCAL word until it reached `target` (wrap-safe).  One thread.
+__device__ __forceinline__ bool wait_local(const McbCtx& c, const uint32_t* word, uint32_t target, int site) {
+  const volatile uint32_t* w = word;
+  if ((int32_t)(*w - target) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if ((int32_t)(*w - target) >= 0) return true;
+    const bool poisoned = *reinterpret_cast<volatile uint32_t*>(c.status) != 0u;
+    if (poisoned || globaltimer_ns() - t0 > c.timeout_ns) {
+      report_error(c, MCB_ERR_TIMEOUT, (uint32_t)site, blockIdx.x, *w, target);
+      return false;
+    }
+  }
+}
+
 }  // namespace mcb

@@ -34,6 +34,7 @@
 #define MCB_SITE_LAYER 11
 #define MCB_SITE_AGV_LL 12       // launch counters of the low-latency paths (no flags used)
 #define MCB_SITE_RSV_LL 13
+#define MCB_SITE_A2A_GO 14       // local hand-over word of the all-to-all combine
 #define MCB_SITE_TEST 15
 
 // Status codes written to status[0] (first error wins; 0 = healthy).

@@ -71,6 +71,8 @@ def parse_args(argv=None):
                    help="dense dispatcher: steps with at most this many tokens over all ranks use "
                         "low-latency flagged packets instead of barrier + multicast (0 = never)")
     p.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch")
+    p.add_argument("--weight-budget-gb", type=float, default=48.0,
+                   help="fused: GPU memory for expert weights; layers share weight sets round-robin beyond it")
     p.add_argument("--resume", action="store_true", help="keep rows already in --out and skip them")
     return p.parse_args(argv)
 
@@ -108,7 +110,7 @@ def build_dispatchers(names, cfg, group, args, device, sms_list):
             specs += A2ADispatcher.heap_specs(cfg, fp8)
         if "fused" in names:
             from moe_comms_benchmarking_b200.parallel.fused import FusedExpertDispatcher
-            specs += FusedExpertDispatcher.heap_specs(cfg)
+            specs += FusedExpertDispatcher.heap_specs(cfg, ll_rows=args.ll_rows)
         heap = SymmetricHeap(group, required_bytes(specs), device, transport=args.transport)
     for n in names:
         if n == "a2a":
@@ -117,7 +119,9 @@ def build_dispatchers(names, cfg, group, args, device, sms_list):
             out.append(DenseDispatcher(cfg, group, heap, num_sms=args.dense_num_sms, pdl=not args.no_pdl,
                                        ll_rows=args.ll_rows))
         elif n == "fused":
-            out.append(FusedExpertDispatcher(cfg, group, heap, pdl=not args.no_pdl))
+            out.append(FusedExpertDispatcher(cfg, group, heap, pdl=not args.no_pdl, ll_rows=args.ll_rows,
+                                             num_layers=1 if args.validate else (args.num_layers or 88),
+                                             weight_budget_gb=args.weight_budget_gb))
         elif n == "nccl":
             from moe_comms_benchmarking_b200.parallel.nccl import NCCLDispatcher
             out.append(NCCLDispatcher(cfg, group))
