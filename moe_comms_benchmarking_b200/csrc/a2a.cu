@@ -139,24 +139,35 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
       }
     } else {
       const int nblk = a.hidden / 128;
-      for (int p0 = 0; p0 < row_packs; p0 += 32) {
-        const int p = p0 + lane;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (p < row_packs) v = ld_v4(xrow + p * 16);
-        // amax over the 16 lanes that hold one 128-element block
-        float amax = pack_absmax(v);
+      for (int p0 = 0; p0 < row_packs; p0 += 32 * 4) {
+        uint4 v[4];
+        uint2 q[4];
+        float scale[4];
 #pragma unroll
-        for (int s = 8; s >= 1; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
-        const float scale = amax > 0.f ? __fdiv_rn(amax, 448.0f) : 1.0f;
-        const uint2 q = quant_pack_e4m3(v, scale);
-        const int blk = p >> 4;
+        for (int u = 0; u < 4; ++u) {
+          const int p = p0 + u * 32 + lane;
+          v[u] = p < row_packs ? ld_v4(xrow + p * 16) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          // amax over the 16 lanes that hold one 128-element block
+          float amax = pack_absmax(v[u]);
+#pragma unroll
+          for (int sh = 8; sh >= 1; sh >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
+          scale[u] = amax > 0.f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+          q[u] = quant_pack_e4m3(v[u], scale[u]);
+        }
         for (int j = 0; j < m; ++j) {
           const uint64_t row = (uint64_t)c.rank * a.cap + L.slot[j];
           uint8_t* peer = c.heap_peer[L.dst[j]];
-          if (p < row_packs) {
-            st_v2(peer + a.recv_x_off + row * a.hidden + (uint64_t)p * 8, q);
-            if ((lane & 15) == 0)
-              st_b32(peer + a.recv_scale_off + (row * nblk + blk) * 4, __float_as_uint(scale));
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int p = p0 + u * 32 + lane;
+            if (p < row_packs) {
+              st_v2(peer + a.recv_x_off + row * a.hidden + (uint64_t)p * 8, q[u]);
+              if ((lane & 15) == 0)
+                st_b32(peer + a.recv_scale_off + (row * nblk + (p >> 4)) * 4, __float_as_uint(scale[u]));
+            }
           }
         }
       }
@@ -261,34 +272,48 @@ __global__ void __launch_bounds__(512) a2a_combine_kernel(const __grid_constant_
       m += __popc(have);
     }
     __syncwarp();
-    for (int p = lane; p < row_packs; p += 32) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      int j = 0;
-      for (; j + 4 <= m; j += 4) {
-        uint4 v[4];
+    // 4 packs per lane x up to 4 destinations = 16 independent peer loads in flight
+    for (int p0 = 0; p0 < row_packs; p0 += 32 * 4) {
+      float acc[4][8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          v[u] = ld_v4_stream(c.heap_peer[L.dst[j + u]] + a.y_off +
-                              ((uint64_t)c.rank * a.cap + L.slot[j + u]) * row_bytes + p * 16);
+      for (int u = 0; u < 4; ++u)
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          acc[0] += bf16_lo(v[u].x); acc[1] += bf16_hi(v[u].x);
-          acc[2] += bf16_lo(v[u].y); acc[3] += bf16_hi(v[u].y);
-          acc[4] += bf16_lo(v[u].z); acc[5] += bf16_hi(v[u].z);
-          acc[6] += bf16_lo(v[u].w); acc[7] += bf16_hi(v[u].w);
+        for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
+      for (int j = 0; j < m; j += 4) {
+        uint4 v[4][4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          if (j + jj < m) {
+            const uint8_t* row = c.heap_peer[L.dst[j + jj]] + a.y_off +
+                                 ((uint64_t)c.rank * a.cap + L.slot[j + jj]) * row_bytes;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int p = p0 + u * 32 + lane;
+              v[jj][u] = p < row_packs ? ld_v4_stream(row + (uint64_t)p * 16) : make_uint4(0, 0, 0, 0);
+            }
+          }
+        }
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          if (j + jj < m) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              acc[u][0] += bf16_lo(v[jj][u].x); acc[u][1] += bf16_hi(v[jj][u].x);
+              acc[u][2] += bf16_lo(v[jj][u].y); acc[u][3] += bf16_hi(v[jj][u].y);
+              acc[u][4] += bf16_lo(v[jj][u].z); acc[u][5] += bf16_hi(v[jj][u].z);
+              acc[u][6] += bf16_lo(v[jj][u].w); acc[u][7] += bf16_hi(v[jj][u].w);
+            }
+          }
         }
       }
-      for (; j < m; ++j) {
-        const uint4 v = ld_v4_stream(c.heap_peer[L.dst[j]] + a.y_off +
-                                     ((uint64_t)c.rank * a.cap + L.slot[j]) * row_bytes + p * 16);
-        acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x);
-        acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
-        acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z);
-        acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int p = p0 + u * 32 + lane;
+        if (p < row_packs)
+          st_v4(out + (uint64_t)t * row_bytes + (uint64_t)p * 16,
+                make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]),
+                           pack_bf16x2(acc[u][4], acc[u][5]), pack_bf16x2(acc[u][6], acc[u][7])));
       }
-      st_v4(out + (uint64_t)t * row_bytes + p * 16,
-            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
-                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7])));
     }
     __syncwarp();
   }

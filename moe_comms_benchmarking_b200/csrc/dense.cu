@@ -208,38 +208,65 @@ __device__ __forceinline__ void agv_ll(const McbCtx& c, const McbAgvArgs& a, int
   if ((int)blockIdx.x >= nb) return;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)nb * blockDim.x;
-  // send
-  for (long long i = tid; i < (long long)n * wpr; i += nthreads) {
-    const int row = (int)(i / wpr);
-    int j = (int)(i - (long long)row * wpr);
-    const int jj = j;
-    int t = 0;
+  // send: 4 independent packets per thread in flight
+  const long long nsend = (long long)n * wpr;
+  for (long long i0 = tid; i0 < nsend; i0 += nthreads * 4) {
+    uint2 d[4];
+    uint64_t off[4];
 #pragma unroll
-    for (int k = 0; k < MCB_MAX_TENSORS - 1; ++k)
-      if (t == k && j >= w[k]) { j -= w[k]; t = k + 1; }
-    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.src[t]) + (uint64_t)row * a.row_bytes[t] + (uint64_t)j * 8;
-    const uint4 pkt = ll_pack(ld_v2(src), flag);
-    const uint64_t off = stage + ((uint64_t)(offset + row) * wpr + jj) * 16;
-    if (c.transport == MCB_TRANSPORT_MULTIMEM) {
-      mm_st_v4(c.heap_mc + off, pkt);
-    } else {
-      for (int k = 0; k < c.world; ++k) {
-        int p = c.rank + 1 + k;
-        if (p >= c.world) p -= c.world;
-        st_v4(c.heap_peer[p] + off, pkt);
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * nthreads;
+      off[u] = ~0ull;
+      if (i < nsend) {
+        const int row = (int)(i / wpr);
+        int j = (int)(i - (long long)row * wpr);
+        const int jj = j;
+        int t = 0;
+#pragma unroll
+        for (int k = 0; k < MCB_MAX_TENSORS - 1; ++k)
+          if (t == k && j >= w[k]) { j -= w[k]; t = k + 1; }
+        d[u] = ld_v2(reinterpret_cast<const uint8_t*>(a.src[t]) + (uint64_t)row * a.row_bytes[t] + (uint64_t)j * 8);
+        off[u] = stage + ((uint64_t)(offset + row) * wpr + jj) * 16;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (off[u] == ~0ull) continue;
+      const uint4 pkt = ll_pack(d[u], flag);
+      if (c.transport == MCB_TRANSPORT_MULTIMEM) {
+        mm_st_v4(c.heap_mc + off[u], pkt);
+      } else {
+        for (int k = 0; k < c.world; ++k) {
+          int p = c.rank + 1 + k;
+          if (p >= c.world) p -= c.world;
+          st_v4(c.heap_peer[p] + off[u], pkt);
+        }
       }
     }
   }
-  // receive
-  for (long long i = tid; i < (long long)valid * wpr; i += nthreads) {
-    const int row = (int)(i / wpr);
-    int j = (int)(i - (long long)row * wpr);
-    const uint2 d = ll_wait(c, c.heap_local + stage + (uint64_t)i * 16, flag, a.site);
-    int t = 0;
+  // receive: poll 4 packets at a time, wait only for those not there yet
+  const long long nrecv = (long long)valid * wpr;
+  for (long long i0 = tid; i0 < nrecv; i0 += nthreads * 4) {
+    uint4 v[4];
 #pragma unroll
-    for (int k = 0; k < MCB_MAX_TENSORS - 1; ++k)
-      if (t == k && j >= w[k]) { j -= w[k]; t = k + 1; }
-    st_v2(c.heap_local + a.dst_off[t] + (uint64_t)row * a.row_bytes[t] + (uint64_t)j * 8, d);
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * nthreads;
+      if (i < nrecv) v[u] = ld_v4_volatile(c.heap_local + stage + (uint64_t)i * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * nthreads;
+      if (i >= nrecv) break;
+      uint2 d = make_uint2(v[u].x, v[u].z);
+      if (v[u].y != flag || v[u].w != flag) d = ll_wait(c, c.heap_local + stage + (uint64_t)i * 16, flag, a.site);
+      const int row = (int)(i / wpr);
+      int j = (int)(i - (long long)row * wpr);
+      int t = 0;
+#pragma unroll
+      for (int k = 0; k < MCB_MAX_TENSORS - 1; ++k)
+        if (t == k && j >= w[k]) { j -= w[k]; t = k + 1; }
+      st_v2(c.heap_local + a.dst_off[t] + (uint64_t)row * a.row_bytes[t] + (uint64_t)j * 8, d);
+    }
   }
 }
 
@@ -370,21 +397,47 @@ __device__ __forceinline__ void rsv_ll(const McbCtx& c, const McbRsvArgs& a, int
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)nb * blockDim.x;
   const uint8_t* mine = c.heap_local + a.src_off;
-  for (long long i = tid; i < (long long)valid * wpr; i += nthreads) {
-    const int g = (int)(i / wpr);
-    const int j = (int)(i - (long long)g * wpr);
-    int owner = 0;
-    while (owner + 1 < c.world && s_prefix[owner + 1] <= g) ++owner;
-    const uint4 pkt = ll_pack(ld_v2(mine + (uint64_t)g * a.row_bytes + (uint64_t)j * 8), flag);
-    st_v4(c.heap_peer[owner] + stage + (uint64_t)c.rank * per_src + ((uint64_t)(g - s_prefix[owner]) * wpr + j) * 16, pkt);
+  // send: 4 independent packets per thread in flight
+  const long long nsend = (long long)valid * wpr;
+  for (long long i0 = tid; i0 < nsend; i0 += nthreads * 4) {
+    uint2 d[4];
+    uint8_t* dst[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * nthreads;
+      dst[u] = nullptr;
+      if (i < nsend) {
+        const int g = (int)(i / wpr);
+        const int j = (int)(i - (long long)g * wpr);
+        int owner = 0;
+        while (owner + 1 < c.world && s_prefix[owner + 1] <= g) ++owner;
+        d[u] = ld_v2(mine + (uint64_t)g * a.row_bytes + (uint64_t)j * 8);
+        dst[u] = c.heap_peer[owner] + stage + (uint64_t)c.rank * per_src +
+                 ((uint64_t)(g - s_prefix[owner]) * wpr + j) * 16;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (dst[u]) st_v4(dst[u], ll_pack(d[u], flag));
   }
+  // receive: read the packets of four sources at a time, wait only for those not there yet
   uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
   for (long long i = tid; i < (long long)n * wpr; i += nthreads) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < c.world; ++s) {
-      const uint2 d = ll_wait(c, c.heap_local + stage + (uint64_t)s * per_src + (uint64_t)i * 16, flag, a.site);
-      acc[0] += bf16_lo(d.x); acc[1] += bf16_hi(d.x);
-      acc[2] += bf16_lo(d.y); acc[3] += bf16_hi(d.y);
+    const uint8_t* slot0 = c.heap_local + stage + (uint64_t)i * 16;
+    for (int s0 = 0; s0 < c.world; s0 += 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (s0 + u < c.world) v[u] = ld_v4_volatile(slot0 + (uint64_t)(s0 + u) * per_src);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (s0 + u >= c.world) break;
+        uint2 d = make_uint2(v[u].x, v[u].z);
+        if (v[u].y != flag || v[u].w != flag) d = ll_wait(c, slot0 + (uint64_t)(s0 + u) * per_src, flag, a.site);
+        acc[0] += bf16_lo(d.x); acc[1] += bf16_hi(d.x);
+        acc[2] += bf16_lo(d.y); acc[3] += bf16_hi(d.y);
+      }
     }
     st_v2(out + (uint64_t)i * 8, make_uint2(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3])));
   }

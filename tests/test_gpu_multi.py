@@ -35,6 +35,27 @@ def test_validate_all_impls_multi_gpu(transport):
     assert f"# VALIDATION PASSED (all {n} ranks)" in res.stdout
 
 
+@pytest.mark.parametrize("transport", ["auto", "p2p"])
+def test_tensor_parallel_collectives_multi_gpu(transport):
+    n = _ngpu()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    n = 4 if n >= 4 else 2
+    res = _torchrun(n, ["-m", "moe_comms_benchmarking_b200.selftest", "--transport", transport])
+    assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-4000:]
+    assert f"# SELFTEST PASSED (all {n} ranks" in res.stdout
+
+
+def test_fused_experts_validate_multi_gpu():
+    n = _ngpu()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    res = _torchrun(2, ["run.py", "--impl", "fused", "--validate", "--num-experts", "64", "--topk", "6",
+                        "--hidden", "512", "--intermediate", "256"])
+    assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-4000:]
+    assert "# VALIDATION PASSED (all 2 ranks)" in res.stdout
+
+
 def test_rank_leaving_between_steps_is_seen_on_the_host(tmp_path):
     """Rank 1 announces that it leaves after step 2 (nothing in flight) and exits; rank 0 reads
     the announcement before its next launch and stops instead of waiting in a kernel.  NVLS is
