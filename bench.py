@@ -46,7 +46,7 @@ def parse_args(argv=None):
     p.add_argument("--global-batch", type=int, default=8192)
     p.add_argument("--sweep", default="1,64,512,4096", help="extra global batches reported under 'sweep'")
     p.add_argument("--no-pdl", action="store_true")
-    p.add_argument("--ll-rows", type=int, default=768)
+    p.add_argument("--ll-rows", type=int, default=-1)
     return p.parse_args(argv)
 
 

@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
   const McbA2ADispatchArgs& a = EMU ? eargs[blockIdx.y] : args_p;
   __shared__ DestList s_list[kMaxWarps];
   __shared__ int s_last;
+  __shared__ int s_m;
   pdl_wait();
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -80,14 +81,22 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
   }
   const int row_packs = a.hidden / 8;  // 16-byte packs of bf16 per row
   const uint8_t* x = reinterpret_cast<const uint8_t*>(a.x);
-  DestList& L = s_list[warp];
-  // Only as many blocks as there are warps' worth of tokens take part (at least one, which
-  // also publishes the counts of a rank without tokens); the others leave at once.
-  int nwork = (n + nwarps - 1) / nwarps;
+  // With no more tokens than blocks, one block serves one token and its warps share the row
+  // (short critical path for wide rows); otherwise one warp serves one token.  Only as many
+  // blocks as that needs take part (at least one, which also publishes the counts of a rank
+  // without tokens); the others leave at once.
+  const bool bmode = n <= (int)gridDim.x;
+  int nwork = bmode ? n : (n + nwarps - 1) / nwarps;
   nwork = nwork < 1 ? 1 : (nwork > (int)gridDim.x ? (int)gridDim.x : nwork);
   if ((int)blockIdx.x >= nwork) return;
+  DestList& L = s_list[bmode ? 0 : warp];
+  const int p_begin = bmode ? warp * 128 : 0;
+  const int p_step = bmode ? nwarps * 128 : 128;
 
-  for (int t = blockIdx.x * nwarps + warp; t < n; t += nwork * nwarps) {
+  for (int t = bmode ? (int)blockIdx.x : (int)blockIdx.x * nwarps + warp; t < n;
+       t += bmode ? (int)gridDim.x : nwork * nwarps) {
+    int m = 0;
+    if (!bmode || warp == 0) {
     // Destination ranks of this token as a bitmask (3 words cover MCB_MAX_RANKS = 72).
     uint32_t m0 = 0, m1 = 0, m2 = 0;
     for (int k = lane; k < a.topk; k += 32) {
@@ -101,7 +110,6 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
     }
     m0 = warp_or(m0); m1 = warp_or(m1); m2 = warp_or(m2);
     // One slot per destination from the local counters; remember it for the combine.
-    int m = 0;
     for (int d0 = 0; d0 < W; d0 += 32) {
       const uint32_t word = d0 == 0 ? m0 : (d0 == 32 ? m1 : m2);
       const int d = d0 + lane;
@@ -116,11 +124,13 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
       }
       m += __popc(have);
     }
-    __syncwarp();
+    if (bmode && lane == 0) s_m = m;
+    }
+    if (bmode) { __syncthreads(); m = s_m; } else { __syncwarp(); }
     const uint8_t* xrow = x + (long long)t * a.hidden * 2;
     if (!a.fp8) {
       const uint64_t row_bytes = (uint64_t)a.hidden * 2;
-      for (int p0 = 0; p0 < row_packs; p0 += 32 * 4) {
+      for (int p0 = p_begin; p0 < row_packs; p0 += p_step) {
         uint4 v[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -139,7 +149,7 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
       }
     } else {
       const int nblk = a.hidden / 128;
-      for (int p0 = 0; p0 < row_packs; p0 += 32 * 4) {
+      for (int p0 = p_begin; p0 < row_packs; p0 += p_step) {
         uint4 v[4];
         uint2 q[4];
         float scale[4];
@@ -173,7 +183,7 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
       }
     }
     // Routing rows (ids, weights) and the source token index travel with the token.
-    for (int k = lane; k < a.topk; k += 32) {
+    for (int k = lane; k < a.topk && (!bmode || warp == 0); k += 32) {
       const long long e = a.topk_idx[(long long)t * a.topk + k];
       const float w = a.topk_w ? a.topk_w[(long long)t * a.topk + k] : 1.0f;
       for (int j = 0; j < m; ++j) {
@@ -183,13 +193,13 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
         *reinterpret_cast<float*>(peer + a.recv_w_off + (row * a.topk + k) * 4) = w;
       }
     }
-    if (lane == 0) {
+    if (lane == 0 && (!bmode || warp == 0)) {
       for (int j = 0; j < m; ++j) {
         const uint64_t row = (uint64_t)c.rank * a.cap + L.slot[j];
         *reinterpret_cast<int*>(c.heap_peer[L.dst[j]] + a.recv_src_off + row * 4) = t;
       }
     }
-    __syncwarp();
+    if (bmode) __syncthreads(); else __syncwarp();
   }
 
   // Grid-wide completion: the last block publishes counts and meets the other ranks.
@@ -231,7 +241,8 @@ __global__ void __launch_bounds__(512) a2a_combine_kernel(const __grid_constant_
   if (n < 0) n = 0;
   if (n > a.cap) n = a.cap;
   const uint32_t launch = next_launch_count(c, MCB_SITE_A2A_COMBINE);
-  int nwork = (n + nwarps - 1) / nwarps;
+  const bool bmode = n <= (int)gridDim.x;      // one block per token, its warps share the row
+  int nwork = bmode ? n : (n + nwarps - 1) / nwarps;
   nwork = nwork < 1 ? 1 : (nwork > (int)gridDim.x ? (int)gridDim.x : nwork);
   if ((int)blockIdx.x >= nwork) return;
   if (W > 1) {
@@ -257,8 +268,11 @@ __global__ void __launch_bounds__(512) a2a_combine_kernel(const __grid_constant_
   const int row_packs = a.hidden / 8;
   const uint64_t row_bytes = (uint64_t)a.hidden * 2;
   uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
-  DestList& L = s_list[warp];
-  for (int t = blockIdx.x * nwarps + warp; t < n; t += nwork * nwarps) {
+  DestList& L = s_list[warp];            // in block mode every warp lists the destinations itself
+  const int p_begin = bmode ? warp * 128 : 0;
+  const int p_step = bmode ? nwarps * 128 : 128;
+  for (int t = bmode ? (int)blockIdx.x : (int)blockIdx.x * nwarps + warp; t < n;
+       t += bmode ? (int)gridDim.x : nwork * nwarps) {
     int m = 0;
     for (int d0 = 0; d0 < W; d0 += 32) {
       const int d = d0 + lane;
@@ -273,7 +287,7 @@ __global__ void __launch_bounds__(512) a2a_combine_kernel(const __grid_constant_
     }
     __syncwarp();
     // 4 packs per lane x up to 4 destinations = 16 independent peer loads in flight
-    for (int p0 = 0; p0 < row_packs; p0 += 32 * 4) {
+    for (int p0 = p_begin; p0 < row_packs; p0 += p_step) {
       float acc[4][8];
 #pragma unroll
       for (int u = 0; u < 4; ++u)

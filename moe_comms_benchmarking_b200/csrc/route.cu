@@ -14,7 +14,7 @@
 
 namespace mcb {
 
-constexpr int kRouteThreads = 256;
+constexpr int kRouteThreads = 1024;
 constexpr int kMaxLocalExperts = 1024;
 constexpr int kSingleBlockEntries = 16384;   // (token, k) entries one block routes alone
 
@@ -30,7 +30,7 @@ __device__ __forceinline__ bool spin_until_ge(const volatile int* p, int target,
 
 // One launch, two phases separated by a "last block computes the offsets" hand-over; blocks of
 // the same launch wait for it on a local counter, so the grid must be co-resident (<= #SMs).
-__global__ void __launch_bounds__(kRouteThreads) route_kernel(const __grid_constant__ McbRouteArgs a) {
+__global__ void __launch_bounds__(kRouteThreads, 1) route_kernel(const __grid_constant__ McbRouteArgs a) {
   __shared__ int s_hist[kMaxLocalExperts];
   __shared__ int s_flag;
   pdl_wait();
@@ -49,9 +49,16 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const __grid_const
     __shared__ int s_cursor[kMaxLocalExperts];
     for (int e = tid; e < E; e += blockDim.x) { s_hist[e] = 0; s_cursor[e] = 0; }
     __syncthreads();
-    for (int i = tid; i < (int)entries; i += blockDim.x) {
-      const long long e = a.topk_idx[i] - a.expert_begin;
-      if (e >= 0 && e < E) atomicAdd(&s_hist[(int)e], 1);
+    for (int i0 = tid; i0 < (int)entries; i0 += blockDim.x * 4) {
+      long long e[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        e[u] = i < (int)entries ? a.topk_idx[i] - a.expert_begin : -1;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (e[u] >= 0 && e[u] < E) atomicAdd(&s_hist[(int)e[u]], 1);
     }
     __syncthreads();
     if (tid == 0) {
@@ -74,19 +81,32 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const __grid_const
       *a.num_m_tiles = tiles < a.max_tiles ? tiles : a.max_tiles;
     }
     __syncthreads();
-    for (int i = tid; i < (int)entries; i += blockDim.x) {
-      const long long e = a.topk_idx[i] - a.expert_begin;
-      int pos = -1;
-      if (e >= 0 && e < E) {
-        pos = s_hist[(int)e] + atomicAdd(&s_cursor[(int)e], 1);
-        if (pos < a.max_pairs) {
-          a.pair_token[pos] = i / a.topk;
-          a.pair_prob[pos] = a.topk_w ? a.topk_w[i] : 1.0f;
-        } else {
-          pos = -1;
-        }
+    for (int i0 = tid; i0 < (int)entries; i0 += blockDim.x * 4) {
+      long long e[4];
+      float w[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        const bool in = i < (int)entries;
+        e[u] = in ? a.topk_idx[i] - a.expert_begin : -1;
+        w[u] = in && a.topk_w ? a.topk_w[i] : 1.0f;
       }
-      a.pair_pos[i] = pos;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i >= (int)entries) break;
+        int pos = -1;
+        if (e[u] >= 0 && e[u] < E) {
+          pos = s_hist[(int)e[u]] + atomicAdd(&s_cursor[(int)e[u]], 1);
+          if (pos < a.max_pairs) {
+            a.pair_token[pos] = i / a.topk;
+            a.pair_prob[pos] = w[u];
+          } else {
+            pos = -1;
+          }
+        }
+        a.pair_pos[i] = pos;
+      }
     }
     return;
   }
@@ -97,9 +117,16 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const __grid_const
   // ---- phase 1: histogram of the entries owned by this block ----
   for (int e = tid; e < E; e += blockDim.x) s_hist[e] = 0;
   __syncthreads();
-  for (long long i = lo + tid; i < hi; i += blockDim.x) {
-    const long long e = a.topk_idx[i] - a.expert_begin;
-    if (e >= 0 && e < E) atomicAdd(&s_hist[(int)e], 1);
+  for (long long i0 = lo + tid; i0 < hi; i0 += blockDim.x * 4) {
+    long long e[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * blockDim.x;
+      e[u] = i < hi ? a.topk_idx[i] - a.expert_begin : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (e[u] >= 0 && e[u] < E) atomicAdd(&s_hist[(int)e[u]], 1);
   }
   __syncthreads();
   for (int e = tid; e < E; e += blockDim.x)
@@ -154,19 +181,31 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const __grid_const
   // ---- phase 2: place every local (token, k) entry into its expert's segment ----
   for (int e = tid; e < E; e += blockDim.x) s_hist[e] = *reinterpret_cast<volatile int*>(&a.expert_offset[e]);
   __syncthreads();
-  for (long long i = lo + tid; i < hi; i += blockDim.x) {
-    const long long e = a.topk_idx[i] - a.expert_begin;
-    int pos = -1;
-    if (e >= 0 && e < E) {
-      pos = s_hist[(int)e] + atomicAdd(&a.expert_cursor[(int)e], 1);
-      if (pos < a.max_pairs) {
-        a.pair_token[pos] = (int)(i / a.topk);
-        a.pair_prob[pos] = a.topk_w ? a.topk_w[i] : 1.0f;
-      } else {
-        pos = -1;
-      }
+  for (long long i0 = lo + tid; i0 < hi; i0 += blockDim.x * 4) {
+    long long e[4];
+    float w[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * blockDim.x;
+      e[u] = i < hi ? a.topk_idx[i] - a.expert_begin : -1;
+      w[u] = i < hi && a.topk_w ? a.topk_w[i] : 1.0f;
     }
-    a.pair_pos[i] = pos;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * blockDim.x;
+      if (i >= hi) break;
+      int pos = -1;
+      if (e[u] >= 0 && e[u] < E) {
+        pos = s_hist[(int)e[u]] + atomicAdd(&a.expert_cursor[(int)e[u]], 1);
+        if (pos < a.max_pairs) {
+          a.pair_token[pos] = (int)(i / a.topk);
+          a.pair_prob[pos] = w[u];
+        } else {
+          pos = -1;
+        }
+      }
+      a.pair_pos[i] = pos;
+    }
   }
   __syncthreads();
   if (tid == 0) {

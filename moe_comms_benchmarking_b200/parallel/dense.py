@@ -25,12 +25,22 @@ from .base import Dispatcher
 from .symm_heap import SymmetricHeap, required_bytes
 
 
+def resolve_ll_rows(cfg: Config, ll_rows: int) -> int:
+    """Row limit of the low-latency packet mode.  ``-1`` picks the measured crossover with the
+    barrier + multicast mode on 8xB200 (about 256 rows at EP=8, 512 at EP=2): min(512, 2048 / EP)."""
+    if cfg.ep_size <= 1:
+        return 0
+    if ll_rows < 0:
+        ll_rows = min(512, 2048 // cfg.ep_size)
+    return min(int(ll_rows), max(cfg.global_cap, 1))
+
+
 class DenseDispatcher(Dispatcher):
     name = "dense"
 
     def __init__(self, cfg: Config, group, heap: SymmetricHeap | None = None, num_sms: int = DEFAULT_GRID,
                  threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto",
-                 combine_dtype=torch.bfloat16, ll_rows: int = 768, device=None):
+                 combine_dtype=torch.bfloat16, ll_rows: int = -1, device=None):
         super().__init__(cfg, group, device)
         self.heap = heap
         self._own_heap = heap is None
@@ -40,18 +50,18 @@ class DenseDispatcher(Dispatcher):
         self.transport = transport
         self.combine_dtype = combine_dtype
         # Low-latency packet mode serves steps that hold at most ll_rows tokens over all ranks.
-        self.ll_rows = min(int(ll_rows), max(cfg.global_cap, 1)) if cfg.ep_size > 1 else 0
+        self.ll_rows = resolve_ll_rows(cfg, ll_rows)
         self.kernel_launches_per_step = lambda nl: 1 + 2 * nl
 
     @staticmethod
     def _ll_bytes(cfg: Config, ll_rows: int):
         H, K = cfg.hidden, cfg.topk
-        ll_rows = min(int(ll_rows), max(cfg.global_cap, 1)) if cfg.ep_size > 1 else 0
+        ll_rows = resolve_ll_rows(cfg, ll_rows)
         return (agv_ll_stage_bytes(ll_rows, [H * 2, K * 8, K * 4]),
                 rsv_ll_stage_bytes(cfg.ep_size, ll_rows, max(cfg.per_rank_cap, 1), H * 2))
 
     @staticmethod
-    def heap_specs(cfg: Config, combine_dtype=torch.bfloat16, ll_rows: int = 768):
+    def heap_specs(cfg: Config, combine_dtype=torch.bfloat16, ll_rows: int = -1):
         g, H, K = max(cfg.global_cap, 1), cfg.hidden, cfg.topk
         a, r = DenseDispatcher._ll_bytes(cfg, ll_rows)
         return [([g, H], torch.bfloat16), ([g, K], torch.int64), ([g, K], torch.float32), ([g, H], combine_dtype),

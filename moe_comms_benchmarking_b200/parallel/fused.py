@@ -25,6 +25,7 @@ from ..ops import _ext, oracle
 from ..ops.dense import AllGatherVPlan, MetadataPlan, DEFAULT_GRID, DEFAULT_THREADS, agv_ll_stage_bytes
 from ..ops.experts import (ExpertCombinePlan, ExpertWeights, GroupedGemmPlan, RouteBuffers, RoutePlan, NUM_SMS)
 from .base import Dispatcher
+from .dense import resolve_ll_rows
 from .symm_heap import SymmetricHeap, required_bytes
 
 
@@ -32,19 +33,19 @@ class FusedExpertDispatcher(Dispatcher):
     name = "fused"
 
     def __init__(self, cfg: Config, group, heap: SymmetricHeap | None = None, num_sms: int = DEFAULT_GRID,
-                 threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto", ll_rows: int = 768,
+                 threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto", ll_rows: int = -1,
                  num_layers: int = 88, weight_budget_gb: float = 64.0, weight_seed: int = 7, device=None):
         super().__init__(cfg, group, device)
         self.heap, self._own_heap = heap, heap is None
         self.num_sms, self.threads, self.pdl, self.transport = int(num_sms), int(threads), bool(pdl), transport
-        self.ll_rows = min(int(ll_rows), max(cfg.global_cap, 1)) if cfg.ep_size > 1 else 0
+        self.ll_rows = resolve_ll_rows(cfg, ll_rows)
         self.num_layers, self.weight_budget_gb, self.weight_seed = num_layers, weight_budget_gb, weight_seed
         self.kernel_launches_per_step = lambda nl: 1 + 5 * nl
 
     @staticmethod
-    def heap_specs(cfg: Config, ll_rows: int = 768):
+    def heap_specs(cfg: Config, ll_rows: int = -1):
         g, H, K = max(cfg.global_cap, 1), cfg.hidden, cfg.topk
-        ll = min(int(ll_rows), g) if cfg.ep_size > 1 else 0
+        ll = resolve_ll_rows(cfg, ll_rows)
         return [([g, H], torch.bfloat16), ([g, K], torch.int64), ([g, K], torch.float32), ([g, H], torch.bfloat16),
                 ([max(agv_ll_stage_bytes(ll, [H * 2, K * 8, K * 4]), 16)], torch.uint8)]
 

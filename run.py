@@ -67,9 +67,9 @@ def parse_args(argv=None):
     p.add_argument("--expert", choices=["identity", "swiglu"], default="identity")
     p.add_argument("--dense-num-sms", type=int, default=148, help="CTA cap of the dense kernels")
     p.add_argument("--transport", choices=["auto", "multimem", "p2p"], default="auto")
-    p.add_argument("--ll-rows", type=int, default=768,
+    p.add_argument("--ll-rows", type=int, default=-1,
                    help="dense dispatcher: steps with at most this many tokens over all ranks use "
-                        "low-latency flagged packets instead of barrier + multicast (0 = never)")
+                        "low-latency flagged packets instead of barrier + multicast (0 = never, -1 = measured default)")
     p.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch")
     p.add_argument("--weight-budget-gb", type=float, default=48.0,
                    help="fused: GPU memory for expert weights; layers share weight sets round-robin beyond it")
