@@ -25,6 +25,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "mcb_combine.cuh"
 #include "mcb_gemm.h"
 #include "mcb_launch.h"
 
@@ -168,8 +169,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(kNumThreads, 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ McbGemmArgs a) {
+__device__ __forceinline__ void gemm_device(const CUtensorMap& w_map, const McbGemmArgs& a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
@@ -351,6 +351,35 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   }
 }
 
+template <int MODE>
+__global__ void __launch_bounds__(kNumThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ McbGemmArgs a) {
+  gemm_device<MODE>(w_map, a);
+}
+
+// FC2 GEMM and the cross-rank combine in ONE kernel: the persistent GEMM CTAs finish their
+// tiles (y = prob * act Wd^T), free their TMEM, meet in a grid-wide barrier (all CTAs are
+// co-resident: the launch is cooperative), and then run the combine: local pre-sum of each
+// token's pairs into the symmetric partial-sum buffer, block-matched cross-GPU barrier,
+// multimem.ld_reduce (or peer loads) of the rows this rank owns.
+__global__ void __launch_bounds__(kNumThreads, 1)
+fc2_combine_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ McbGemmArgs a,
+                   const __grid_constant__ McbCtx c, const __grid_constant__ McbCombineArgs cmb) {
+  gemm_device<MCB_GEMM_FC2>(w_map, a);
+  // grid-wide barrier: every CTA's y rows are written before any CTA sums them
+  const uint32_t launch = next_launch_count(c, MCB_SITE_FUSED_FC1);
+  uint32_t* arrivals = epoch_ptr(c, MCB_SITE_LAYER, 0);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(arrivals, 1u);
+    wait_local(c, arrivals, launch * gridDim.x, MCB_SITE_LAYER);
+    __threadfence();
+  }
+  __syncthreads();
+  combine_body(c, cmb);
+}
+
 }  // namespace mcb
 
 using namespace mcb;
@@ -387,19 +416,34 @@ int mcb_make_weight_tmap(void* out, const void* base, uint64_t rows, uint64_t co
   return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+static bool configure_gemm_kernels() {
+  static int state = 0;   // 0 = not tried, 1 = ok, -1 = failed
+  if (state == 0) {
+    cudaError_t e1 = cudaFuncSetAttribute(grouped_gemm_kernel<MCB_GEMM_FC1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e2 = cudaFuncSetAttribute(grouped_gemm_kernel<MCB_GEMM_FC2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e3 = cudaFuncSetAttribute(fc2_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    state = (e1 == cudaSuccess && e2 == cudaSuccess && e3 == cudaSuccess) ? 1 : -1;
+  }
+  return state == 1;
+}
+
+// FC2 + combine in one cooperative launch (grid <= number of SMs; one CTA per SM).
+int mcb_launch_fc2_combine(const void* tmap, const McbGemmArgs* args, const McbCtx* ctx, const McbCombineArgs* cmb,
+                           int grid, cudaStream_t stream) {
+  if (grid < 1 || grid > MCB_MAX_BLOCKS || !tmap || !args || !ctx || !cmb) return cudaErrorInvalidValue;
+  if (args->k_total % kBlockK || args->k_total < kBlockK || args->n_total % kBlockN) return cudaErrorInvalidValue;
+  if ((args->a_row_bytes & 15) || (args->out_row_bytes & 15) || cmb->hidden % 8) return cudaErrorInvalidValue;
+  if (!configure_gemm_kernels()) return cudaErrorUnknown;
+  const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(tmap);
+  return launch_kernel(fc2_combine_kernel, dim3(grid), dim3(kNumThreads), kSmemBytes, stream, 0, true, map, *args, *ctx, *cmb);
+}
+
 int mcb_launch_grouped_gemm(const void* tmap, const McbGemmArgs* args, int mode, int grid, int pdl, cudaStream_t stream) {
   if (grid < 1 || !tmap || !args) return cudaErrorInvalidValue;
   if (args->k_total % kBlockK || args->k_total < kBlockK) return cudaErrorInvalidValue;
   if (mode == MCB_GEMM_FC1 ? (args->n_total % 256) : (args->n_total % kBlockN)) return cudaErrorInvalidValue;
   if ((args->a_row_bytes & 15) || (args->out_row_bytes & 15)) return cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e1 = cudaFuncSetAttribute(grouped_gemm_kernel<MCB_GEMM_FC1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    cudaError_t e2 = cudaFuncSetAttribute(grouped_gemm_kernel<MCB_GEMM_FC2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e1 != cudaSuccess) return (int)e1;
-    if (e2 != cudaSuccess) return (int)e2;
-    configured = true;
-  }
+  if (!configure_gemm_kernels()) return cudaErrorUnknown;
   const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(tmap);
   if (mode == MCB_GEMM_FC1)
     return launch_kernel(grouped_gemm_kernel<MCB_GEMM_FC1>, dim3(grid), dim3(kNumThreads), kSmemBytes, stream, pdl, false, map, *args);

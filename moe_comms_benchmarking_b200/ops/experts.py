@@ -161,3 +161,22 @@ class ExpertCombinePlan:
         lib = _ext.require()
         _ext.check(lib.mcb_launch_combine(C.byref(self.heap.ctx()), C.byref(self.args), self.grid, self.threads,
                                           int(pdl), _ext.stream_handle(stream)), "expert_combine")
+
+
+class Fc2CombinePlan:
+    """FC2 grouped GEMM and the cross-rank combine as ONE cooperative kernel launch
+    (``fc2_combine_kernel``): GEMM tiles, grid-wide barrier, local pre-sum, cross-GPU barrier,
+    switch-side reduction.  Built from the two stand-alone plans so both forms share arguments."""
+
+    def __init__(self, heap: SymmetricHeap, fc2: GroupedGemmPlan, combine: ExpertCombinePlan, grid: int = NUM_SMS):
+        if fc2.mode != _ext.GEMM_FC2:
+            raise ValueError("Fc2CombinePlan needs an FC2 plan")
+        if not (1 <= grid <= NUM_SMS):
+            raise ValueError("the fused kernel needs all its blocks resident at once: grid <= number of SMs")
+        self.heap, self.fc2, self.combine, self.grid = heap, fc2, combine, grid
+
+    def launch(self, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        _ext.check(lib.mcb_launch_fc2_combine(C.c_void_p(self.fc2.tmap[1]), C.byref(self.fc2.args),
+                                              C.byref(self.heap.ctx()), C.byref(self.combine.args), self.grid,
+                                              _ext.stream_handle(stream)), "fc2_combine")

@@ -11,6 +11,10 @@ expert computation the transport exists for.  Per layer and rank:
     FC2        y = prob * (act Wd^T)                              csrc/gemm.cu    grouped_gemm_kernel<FC2>
     combine    out[t] = sum_ranks sum_local-pairs y               csrc/route.cu   combine_kernel
 
+By default FC2 and the combine are ONE kernel (``fc2_combine_kernel`` in csrc/gemm.cu: the GEMM
+CTAs finish their tiles, meet in a grid-wide barrier and run the combine, multimem.ld_reduce
+included); ``fuse_combine=False`` launches them separately.
+
 Weights: 512 experts x 3 x 1024^2 bf16 is 3.2 GB per layer; every layer gets its own set while
 they fit in ``weight_budget_gb`` per GPU, after which sets are reused round-robin (each set is
 far larger than L2, so a layer still streams its weights from HBM).
@@ -23,7 +27,8 @@ import torch.distributed as dist
 from ..config import Config
 from ..ops import _ext, oracle
 from ..ops.dense import AllGatherVPlan, MetadataPlan, DEFAULT_GRID, DEFAULT_THREADS, agv_ll_stage_bytes
-from ..ops.experts import (ExpertCombinePlan, ExpertWeights, GroupedGemmPlan, RouteBuffers, RoutePlan, NUM_SMS)
+from ..ops.experts import (ExpertCombinePlan, ExpertWeights, Fc2CombinePlan, GroupedGemmPlan, RouteBuffers, RoutePlan,
+                           NUM_SMS)
 from .base import Dispatcher
 from .dense import resolve_ll_rows
 from .symm_heap import SymmetricHeap, required_bytes
@@ -34,13 +39,15 @@ class FusedExpertDispatcher(Dispatcher):
 
     def __init__(self, cfg: Config, group, heap: SymmetricHeap | None = None, num_sms: int = DEFAULT_GRID,
                  threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto", ll_rows: int = -1,
-                 num_layers: int = 88, weight_budget_gb: float = 64.0, weight_seed: int = 7, device=None):
+                 num_layers: int = 88, weight_budget_gb: float = 64.0, weight_seed: int = 7,
+                 fuse_combine: bool = True, device=None):
         super().__init__(cfg, group, device)
         self.heap, self._own_heap = heap, heap is None
         self.num_sms, self.threads, self.pdl, self.transport = int(num_sms), int(threads), bool(pdl), transport
         self.ll_rows = resolve_ll_rows(cfg, ll_rows)
         self.num_layers, self.weight_budget_gb, self.weight_seed = num_layers, weight_budget_gb, weight_seed
-        self.kernel_launches_per_step = lambda nl: 1 + 5 * nl
+        self.fuse_combine = bool(fuse_combine)
+        self.kernel_launches_per_step = lambda nl: 1 + (4 if self.fuse_combine else 5) * nl
 
     @staticmethod
     def heap_specs(cfg: Config, ll_rows: int = -1):
@@ -91,6 +98,7 @@ class FusedExpertDispatcher(Dispatcher):
                     for w in self.weights]
         self.combine_plan = ExpertCombinePlan(h, self.y, self.route, self.partial, self.out_buf, self.n_local,
                                               self.step_metadata, cap, grid=NUM_SMS)
+        self.fc2_combine = [Fc2CombinePlan(h, f, self.combine_plan) for f in self.fc2]
         torch.cuda.synchronize()
         dist.barrier(self.group)
         self._built = True
@@ -127,8 +135,14 @@ class FusedExpertDispatcher(Dispatcher):
 
     def layer(self, layer: int = 0):
         self.dispatch()
-        self.experts(layer)
-        self.combine()
+        if self.fuse_combine:
+            s = layer % len(self.weights)
+            self.route_plan.launch(self.pdl)
+            self.fc1[s].launch(self.pdl)
+            self.fc2_combine[s].launch()
+        else:
+            self.experts(layer)
+            self.combine()
 
     def step(self):
         self.layer(0)
