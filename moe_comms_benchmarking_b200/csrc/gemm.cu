@@ -429,13 +429,13 @@ static bool configure_gemm_kernels() {
 
 // FC2 + combine in one cooperative launch (grid <= number of SMs; one CTA per SM).
 int mcb_launch_fc2_combine(const void* tmap, const McbGemmArgs* args, const McbCtx* ctx, const McbCombineArgs* cmb,
-                           int grid, cudaStream_t stream) {
+                           int grid, int pdl, cudaStream_t stream) {
   if (grid < 1 || grid > MCB_MAX_BLOCKS || !tmap || !args || !ctx || !cmb) return cudaErrorInvalidValue;
   if (args->k_total % kBlockK || args->k_total < kBlockK || args->n_total % kBlockN) return cudaErrorInvalidValue;
   if ((args->a_row_bytes & 15) || (args->out_row_bytes & 15) || cmb->hidden % 8) return cudaErrorInvalidValue;
   if (!configure_gemm_kernels()) return cudaErrorUnknown;
   const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(tmap);
-  return launch_kernel(fc2_combine_kernel, dim3(grid), dim3(kNumThreads), kSmemBytes, stream, 0, true, map, *args, *ctx, *cmb);
+  return launch_kernel(fc2_combine_kernel, dim3(grid), dim3(kNumThreads), kSmemBytes, stream, pdl, true, map, *args, *ctx, *cmb);
 }
 
 int mcb_launch_grouped_gemm(const void* tmap, const McbGemmArgs* args, int mode, int grid, int pdl, cudaStream_t stream) {

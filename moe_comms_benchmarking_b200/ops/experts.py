@@ -179,4 +179,4 @@ class Fc2CombinePlan:
         lib = _ext.require()
         _ext.check(lib.mcb_launch_fc2_combine(C.c_void_p(self.fc2.tmap[1]), C.byref(self.fc2.args),
                                               C.byref(self.heap.ctx()), C.byref(self.combine.args), self.grid,
-                                              _ext.stream_handle(stream)), "fc2_combine")
+                                              int(pdl), _ext.stream_handle(stream)), "fc2_combine")

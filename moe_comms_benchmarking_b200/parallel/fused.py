@@ -40,13 +40,14 @@ class FusedExpertDispatcher(Dispatcher):
     def __init__(self, cfg: Config, group, heap: SymmetricHeap | None = None, num_sms: int = DEFAULT_GRID,
                  threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto", ll_rows: int = -1,
                  num_layers: int = 88, weight_budget_gb: float = 64.0, weight_seed: int = 7,
-                 fuse_combine: bool = True, device=None):
+                 fuse_combine: bool = True, coop_pdl: bool = False, device=None):
         super().__init__(cfg, group, device)
         self.heap, self._own_heap = heap, heap is None
         self.num_sms, self.threads, self.pdl, self.transport = int(num_sms), int(threads), bool(pdl), transport
         self.ll_rows = resolve_ll_rows(cfg, ll_rows)
         self.num_layers, self.weight_budget_gb, self.weight_seed = num_layers, weight_budget_gb, weight_seed
         self.fuse_combine = bool(fuse_combine)
+        self.coop_pdl = bool(coop_pdl)   # cooperative + programmatic dependent launch on the fused kernel
         self.kernel_launches_per_step = lambda nl: 1 + (4 if self.fuse_combine else 5) * nl
 
     @staticmethod
@@ -139,7 +140,7 @@ class FusedExpertDispatcher(Dispatcher):
             s = layer % len(self.weights)
             self.route_plan.launch(self.pdl)
             self.fc1[s].launch(self.pdl)
-            self.fc2_combine[s].launch()
+            self.fc2_combine[s].launch(self.pdl and self.coop_pdl)
         else:
             self.experts(layer)
             self.combine()
