@@ -192,7 +192,7 @@ __device__ __forceinline__ bool agv_ll_eligible(const McbCtx& c, const McbAgvArg
 
 // Low-latency all-gather-V: send my rows as packets to every rank's staging area, then poll my
 // own staging area for all `valid` rows and unpack them into the gathered tensors.
-__device__ __forceinline__ void agv_ll(const McbCtx& c, const McbAgvArgs& a, int n, int offset, int valid,
+__device__ __noinline__ void agv_ll(const McbCtx& c, const McbAgvArgs& a, int n, int offset, int valid,
                                        uint32_t flag) {
   int w[MCB_MAX_TENSORS];
   int wpr = 0;
@@ -387,7 +387,7 @@ __device__ __forceinline__ uint4 p2p_reduce_pack(const McbCtx& c, uint64_t off) 
 
 // Low-latency reduce-scatter-V (bf16): push every valid row of my partial sums to its owner as
 // packets, then sum, for each of my own rows, the packets of all ranks in rank order (fp32).
-__device__ __forceinline__ void rsv_ll(const McbCtx& c, const McbRsvArgs& a, int n, int offset, int valid,
+__device__ __noinline__ void rsv_ll(const McbCtx& c, const McbRsvArgs& a, int n, int offset, int valid,
                                        uint32_t flag, const int* s_prefix) {
   const int wpr = (int)(a.row_bytes >> 3);
   const uint64_t per_src = (uint64_t)a.ll_src_rows * wpr * 16;
@@ -444,7 +444,7 @@ __device__ __forceinline__ void rsv_ll(const McbCtx& c, const McbRsvArgs& a, int
 }
 
 template <bool EMU>
-__global__ void __launch_bounds__(512) rsv_kernel(const __grid_constant__ McbCtx ctx_p,
+__global__ void __launch_bounds__(512, 2) rsv_kernel(const __grid_constant__ McbCtx ctx_p,
                                                    const __grid_constant__ McbRsvArgs args_p,
                                                    const McbCtx* ectx, const McbRsvArgs* eargs) {
   const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;

@@ -44,7 +44,8 @@ class DenseDispatcher(Dispatcher):
         super().__init__(cfg, group, device)
         self.heap = heap
         self._own_heap = heap is None
-        self.num_sms = int(num_sms)
+        # A world of one is a local copy: two blocks per SM keep more bytes in flight (measured).
+        self.num_sms = int(num_sms) * (2 if cfg.ep_size == 1 and int(num_sms) == DEFAULT_GRID else 1)
         self.threads = int(threads)
         self.pdl = bool(pdl)
         self.transport = transport
@@ -110,7 +111,8 @@ class DenseDispatcher(Dispatcher):
                                            ll_stage=self.ll_rsv, ll_rows=self.ll_rows)
 
     def set_num_sms(self, num_sms: int):
-        self.num_sms = int(num_sms)
+        # A world of one is a local copy: two blocks per SM keep more bytes in flight (measured).
+        self.num_sms = int(num_sms) * (2 if cfg.ep_size == 1 and int(num_sms) == DEFAULT_GRID else 1)
         if self._built:
             self._make_plans()
 

@@ -10,6 +10,7 @@ share the one scratch array.  Collected last on purpose, so that a run that stop
 failure has already exercised everything else.
 """
 import ctypes as C
+import gc
 
 import pytest
 import torch
@@ -61,12 +62,19 @@ def test_no_alloc_dispatch_matches_the_ordinary_entry_point(world1, lib):
         d.bufs.slot_map.fill_(-7)
         mine = _ext.McbA2ADispatchArgs.from_buffer_copy(args)
         mine.send_count = poisoned.data_ptr()
-        before = torch.cuda.memory_allocated()
-        rc = lib.mcb_a2a_dispatch_noalloc(C.byref(d.heap.ctx()), C.byref(mine), d.num_sms, d.threads,
-                                          _ext.stream_handle())
-        assert rc == 0, lib.mcb_noalloc_last_error().decode()
-        torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        # Objects left over from earlier tests must not be collected (and their GPU memory
+        # freed) inside the window in which the allocator's counter is compared.
+        gc.collect()
+        gc.disable()
+        try:
+            before = torch.cuda.memory_allocated()
+            rc = lib.mcb_a2a_dispatch_noalloc(C.byref(d.heap.ctx()), C.byref(mine), d.num_sms, d.threads,
+                                              _ext.stream_handle())
+            assert rc == 0, lib.mcb_noalloc_last_error().decode()
+            torch.cuda.synchronize()
+            assert torch.cuda.memory_allocated() == before
+        finally:
+            gc.enable()
         got = _received(d.bufs, n)
         assert got[0] == want[0], f"call {call}: row count"
         for g, x in zip(got[1:], want[1:]):
