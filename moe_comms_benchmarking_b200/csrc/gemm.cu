@@ -26,8 +26,10 @@
 #include <stdint.h>
 
 #include "mcb_combine.cuh"
+#include "mcb_dense.cuh"
 #include "mcb_gemm.h"
 #include "mcb_launch.h"
+#include "mcb_route.cuh"
 
 namespace mcb {
 
@@ -357,6 +359,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   gemm_device<MODE>(w_map, a);
 }
 
+// Grid-wide barrier of a cooperative launch: `arrivals` only ever grows; the caller passes
+// the total it must reach (a multiple of the grid size derived from its launch counter).
+__device__ __forceinline__ void grid_sync(const McbCtx& c, uint32_t* arrivals, uint32_t target) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(arrivals, 1u);
+    wait_local(c, arrivals, target, MCB_SITE_LAYER);
+    __threadfence();
+  }
+  __syncthreads();
+}
+
+// Dispatch, routing and FC1 in ONE kernel: every CTA first pushes its share of this rank's
+// tokens to all ranks (multimem.st or flagged packets) and meets the other ranks; after a
+// grid-wide barrier the gathered routing is turned into pair lists and row tiles; after a second
+// one the same CTAs run the grouped FC1 GEMM, gathering token rows straight from the buffer the
+// peers just filled.
+__global__ void __launch_bounds__(kNumThreads, 1)
+dispatch_route_fc1_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ McbGemmArgs a,
+                          const __grid_constant__ McbCtx c, const __grid_constant__ McbAgvArgs agv,
+                          const __grid_constant__ McbRouteArgs r) {
+  agv_device(c, agv);
+  const uint32_t launch = next_launch_count(c, MCB_SITE_FC1_FUSED);
+  uint32_t* arrivals = epoch_ptr(c, MCB_SITE_LAYER, 1);
+  grid_sync(c, arrivals, (2u * launch - 1u) * gridDim.x);
+  route_device(r);
+  grid_sync(c, arrivals, 2u * launch * gridDim.x);
+  gemm_device<MCB_GEMM_FC1>(w_map, a);
+}
+
 // FC2 GEMM and the cross-rank combine in ONE kernel: the persistent GEMM CTAs finish their
 // tiles (y = prob * act Wd^T), free their TMEM, meet in a grid-wide barrier (all CTAs are
 // co-resident: the launch is cooperative), and then run the combine: local pre-sum of each
@@ -368,15 +401,7 @@ fc2_combine_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   gemm_device<MCB_GEMM_FC2>(w_map, a);
   // grid-wide barrier: every CTA's y rows are written before any CTA sums them
   const uint32_t launch = next_launch_count(c, MCB_SITE_FUSED_FC1);
-  uint32_t* arrivals = epoch_ptr(c, MCB_SITE_LAYER, 0);
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(arrivals, 1u);
-    wait_local(c, arrivals, launch * gridDim.x, MCB_SITE_LAYER);
-    __threadfence();
-  }
-  __syncthreads();
+  grid_sync(c, epoch_ptr(c, MCB_SITE_LAYER, 0), launch * gridDim.x);
   combine_body(c, cmb);
 }
 
@@ -422,7 +447,8 @@ static bool configure_gemm_kernels() {
     cudaError_t e1 = cudaFuncSetAttribute(grouped_gemm_kernel<MCB_GEMM_FC1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     cudaError_t e2 = cudaFuncSetAttribute(grouped_gemm_kernel<MCB_GEMM_FC2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     cudaError_t e3 = cudaFuncSetAttribute(fc2_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    state = (e1 == cudaSuccess && e2 == cudaSuccess && e3 == cudaSuccess) ? 1 : -1;
+    cudaError_t e4 = cudaFuncSetAttribute(dispatch_route_fc1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    state = (e1 == cudaSuccess && e2 == cudaSuccess && e3 == cudaSuccess && e4 == cudaSuccess) ? 1 : -1;
   }
   return state == 1;
 }
@@ -436,6 +462,19 @@ int mcb_launch_fc2_combine(const void* tmap, const McbGemmArgs* args, const McbC
   if (!configure_gemm_kernels()) return cudaErrorUnknown;
   const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(tmap);
   return launch_kernel(fc2_combine_kernel, dim3(grid), dim3(kNumThreads), kSmemBytes, stream, pdl, true, map, *args, *ctx, *cmb);
+}
+
+// Dispatch + routing + FC1 in one cooperative launch (grid <= number of SMs).
+int mcb_launch_dispatch_route_fc1(const void* tmap, const McbGemmArgs* args, const McbCtx* ctx, const McbAgvArgs* agv,
+                                  const McbRouteArgs* route, int grid, int pdl, cudaStream_t stream) {
+  if (grid < 1 || grid > MCB_MAX_BLOCKS || !tmap || !args || !ctx || !agv || !route) return cudaErrorInvalidValue;
+  if (args->k_total % kBlockK || args->k_total < kBlockK || args->n_total % 256) return cudaErrorInvalidValue;
+  if ((args->a_row_bytes & 15) || (args->out_row_bytes & 15)) return cudaErrorInvalidValue;
+  if (route->num_local_experts < 1 || route->num_local_experts > kMaxLocalExperts) return cudaErrorInvalidValue;
+  if (!configure_gemm_kernels()) return cudaErrorUnknown;
+  const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(tmap);
+  return launch_kernel(dispatch_route_fc1_kernel, dim3(grid), dim3(kNumThreads), kSmemBytes, stream, pdl, true, map,
+                       *args, *ctx, *agv, *route);
 }
 
 int mcb_launch_grouped_gemm(const void* tmap, const McbGemmArgs* args, int mode, int grid, int pdl, cudaStream_t stream) {

@@ -12,7 +12,7 @@
 
 #define MCB_MAX_RANKS 72      // one NVL72 NVLink domain
 #define MCB_MAX_BLOCKS 512    // flag slots per barrier site
-#define MCB_NUM_SITES 16      // independent barrier sites
+#define MCB_NUM_SITES 24      // independent barrier sites / counter rows
 #define MCB_STATUS_WORDS 8
 
 // Transports for the cross-GPU part of a kernel.
@@ -36,6 +36,7 @@
 #define MCB_SITE_RSV_LL 13
 #define MCB_SITE_A2A_GO 14       // local hand-over word of the all-to-all combine
 #define MCB_SITE_TEST 15
+#define MCB_SITE_FC1_FUSED 16     // per-block launch counters of the fused dispatch + routing + FC1 kernel
 
 // Status codes written to status[0] (first error wins; 0 = healthy).
 #define MCB_OK 0

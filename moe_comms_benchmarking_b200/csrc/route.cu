@@ -11,214 +11,15 @@
 #include "mcb_barrier.cuh"
 #include "mcb_combine.cuh"
 #include "mcb_gemm.h"
+#include "mcb_route.cuh"
 #include "mcb_launch.h"
 
 namespace mcb {
 
-constexpr int kRouteThreads = 1024;
-constexpr int kMaxLocalExperts = 1024;
-constexpr int kSingleBlockEntries = 16384;   // (token, k) entries one block routes alone
-
-__device__ __forceinline__ bool spin_until_ge(const volatile int* p, int target, uint64_t timeout_ns) {
-  if (*p - target >= 0) return true;
-  uint64_t t0 = globaltimer_ns();
-  for (;;) {
-    for (int i = 0; i < 64; ++i)
-      if (*p - target >= 0) return true;
-    if (globaltimer_ns() - t0 > timeout_ns) return false;
-  }
-}
-
-// One launch, two phases separated by a "last block computes the offsets" hand-over; blocks of
-// the same launch wait for it on a local counter, so the grid must be co-resident (<= #SMs).
 __global__ void __launch_bounds__(kRouteThreads, 1) route_kernel(const __grid_constant__ McbRouteArgs a) {
-  __shared__ int s_hist[kMaxLocalExperts];
-  __shared__ int s_flag;
   pdl_wait();
   pdl_launch_dependents();
-  const int tid = threadIdx.x;
-  const int E = a.num_local_experts;
-  int T = *a.num_tokens;
-  if (T < 0) T = 0;
-  if (T > a.max_tokens) T = a.max_tokens;
-  const int ready_base = *reinterpret_cast<volatile int*>(&a.sync[2]);   // stable until this launch's hand-over
-  const long long entries = (long long)T * a.topk;
-  if (entries <= kSingleBlockEntries) {
-    // Small step: block 0 does everything in shared memory (no hand-over between blocks, no
-    // global atomics), the other blocks leave at once.
-    if (blockIdx.x != 0) return;
-    __shared__ int s_cursor[kMaxLocalExperts];
-    for (int e = tid; e < E; e += blockDim.x) { s_hist[e] = 0; s_cursor[e] = 0; }
-    __syncthreads();
-    for (int i0 = tid; i0 < (int)entries; i0 += blockDim.x * 4) {
-      long long e[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * blockDim.x;
-        e[u] = i < (int)entries ? a.topk_idx[i] - a.expert_begin : -1;
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (e[u] >= 0 && e[u] < E) atomicAdd(&s_hist[(int)e[u]], 1);
-    }
-    __syncthreads();
-    if (tid == 0) {
-      int run = 0, tiles = 0;
-      for (int e = 0; e < E; ++e) {
-        const int c = s_hist[e];
-        s_hist[e] = run;
-        a.expert_offset[e] = run;
-        for (int r0 = 0; r0 < c; r0 += 128) {
-          if (tiles < a.max_tiles) {
-            a.tile_expert[tiles] = e;
-            a.tile_row0[tiles] = run + r0;
-            a.tile_rows[tiles] = c - r0 < 128 ? c - r0 : 128;
-          }
-          ++tiles;
-        }
-        run += c;
-      }
-      a.expert_offset[E] = run;
-      *a.num_m_tiles = tiles < a.max_tiles ? tiles : a.max_tiles;
-    }
-    __syncthreads();
-    for (int i0 = tid; i0 < (int)entries; i0 += blockDim.x * 4) {
-      long long e[4];
-      float w[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * blockDim.x;
-        const bool in = i < (int)entries;
-        e[u] = in ? a.topk_idx[i] - a.expert_begin : -1;
-        w[u] = in && a.topk_w ? a.topk_w[i] : 1.0f;
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * blockDim.x;
-        if (i >= (int)entries) break;
-        int pos = -1;
-        if (e[u] >= 0 && e[u] < E) {
-          pos = s_hist[(int)e[u]] + atomicAdd(&s_cursor[(int)e[u]], 1);
-          if (pos < a.max_pairs) {
-            a.pair_token[pos] = i / a.topk;
-            a.pair_prob[pos] = w[u];
-          } else {
-            pos = -1;
-          }
-        }
-        a.pair_pos[i] = pos;
-      }
-    }
-    return;
-  }
-  const long long per_block = (entries + gridDim.x - 1) / gridDim.x;
-  const long long lo = per_block * blockIdx.x;
-  const long long hi = lo + per_block < entries ? lo + per_block : entries;
-
-  // ---- phase 1: histogram of the entries owned by this block ----
-  for (int e = tid; e < E; e += blockDim.x) s_hist[e] = 0;
-  __syncthreads();
-  for (long long i0 = lo + tid; i0 < hi; i0 += blockDim.x * 4) {
-    long long e[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const long long i = i0 + u * blockDim.x;
-      e[u] = i < hi ? a.topk_idx[i] - a.expert_begin : -1;
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-      if (e[u] >= 0 && e[u] < E) atomicAdd(&s_hist[(int)e[u]], 1);
-  }
-  __syncthreads();
-  for (int e = tid; e < E; e += blockDim.x)
-    if (s_hist[e]) atomicAdd(&a.expert_count[e], s_hist[e]);
-  __syncthreads();
-  if (tid == 0) {
-    __threadfence();
-    s_flag = (atomicAdd(&a.sync[0], 1) == (int)gridDim.x - 1);
-    __threadfence();
-  }
-  __syncthreads();
-  if (s_flag) {
-    // Last block: exclusive prefix over experts, row-tile table, then release the others.
-    for (int e = tid; e < E; e += blockDim.x) s_hist[e] = *reinterpret_cast<volatile int*>(&a.expert_count[e]);
-    __syncthreads();
-    if (tid == 0) {
-      int run = 0, tiles = 0;
-      for (int e = 0; e < E; ++e) {
-        const int c = s_hist[e];
-        a.expert_offset[e] = run;
-        for (int r0 = 0; r0 < c; r0 += 128) {
-          if (tiles < a.max_tiles) {
-            a.tile_expert[tiles] = e;
-            a.tile_row0[tiles] = run + r0;
-            a.tile_rows[tiles] = c - r0 < 128 ? c - r0 : 128;
-          }
-          ++tiles;
-        }
-        run += c;
-      }
-      a.expert_offset[E] = run;
-      if (tiles > a.max_tiles || run > a.max_pairs) {
-        if (a.status && atomicCAS(a.status, 0u, (uint32_t)MCB_ERR_CAPACITY) == 0u) {
-          a.status[1] = 100; a.status[2] = (uint32_t)tiles; a.status[3] = (uint32_t)run;
-        }
-        tiles = tiles > a.max_tiles ? a.max_tiles : tiles;
-      }
-      *a.num_m_tiles = tiles;
-      a.sync[0] = 0;
-      __threadfence();
-      atomicAdd(&a.sync[2], 1);
-    }
-  }
-  if (tid == 0) {
-    if (!spin_until_ge(reinterpret_cast<volatile int*>(&a.sync[2]), ready_base + 1, a.timeout_ns)) {
-      if (a.status && atomicCAS(a.status, 0u, (uint32_t)MCB_ERR_TIMEOUT) == 0u) { a.status[1] = 101; a.status[2] = blockIdx.x; }
-    }
-    __threadfence();
-  }
-  __syncthreads();
-
-  // ---- phase 2: place every local (token, k) entry into its expert's segment ----
-  for (int e = tid; e < E; e += blockDim.x) s_hist[e] = *reinterpret_cast<volatile int*>(&a.expert_offset[e]);
-  __syncthreads();
-  for (long long i0 = lo + tid; i0 < hi; i0 += blockDim.x * 4) {
-    long long e[4];
-    float w[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const long long i = i0 + u * blockDim.x;
-      e[u] = i < hi ? a.topk_idx[i] - a.expert_begin : -1;
-      w[u] = i < hi && a.topk_w ? a.topk_w[i] : 1.0f;
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const long long i = i0 + u * blockDim.x;
-      if (i >= hi) break;
-      int pos = -1;
-      if (e[u] >= 0 && e[u] < E) {
-        pos = s_hist[(int)e[u]] + atomicAdd(&a.expert_cursor[(int)e[u]], 1);
-        if (pos < a.max_pairs) {
-          a.pair_token[pos] = (int)(i / a.topk);
-          a.pair_prob[pos] = w[u];
-        } else {
-          pos = -1;
-        }
-      }
-      a.pair_pos[i] = pos;
-    }
-  }
-  __syncthreads();
-  if (tid == 0) {
-    __threadfence();
-    s_flag = (atomicAdd(&a.sync[1], 1) == (int)gridDim.x - 1);
-  }
-  __syncthreads();
-  if (s_flag) {
-    // Last block out: scratch back to zero for the next launch.
-    for (int e = tid; e < E; e += blockDim.x) { a.expert_count[e] = 0; a.expert_cursor[e] = 0; }
-    if (tid == 0) a.sync[1] = 0;
-  }
+  route_device(a);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -13,7 +13,7 @@ from pathlib import Path
 
 MAX_RANKS = 72
 MAX_BLOCKS = 512
-NUM_SITES = 16
+NUM_SITES = 24
 STATUS_WORDS = 8
 MAX_TENSORS = 4
 

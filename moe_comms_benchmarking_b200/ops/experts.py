@@ -180,3 +180,24 @@ class Fc2CombinePlan:
         _ext.check(lib.mcb_launch_fc2_combine(C.c_void_p(self.fc2.tmap[1]), C.byref(self.fc2.args),
                                               C.byref(self.heap.ctx()), C.byref(self.combine.args), self.grid,
                                               int(pdl), _ext.stream_handle(stream)), "fc2_combine")
+
+
+class DispatchRouteFc1Plan:
+    """All-gather-V dispatch, routing and the FC1 grouped GEMM as ONE cooperative kernel launch
+    (``dispatch_route_fc1_kernel``): multicast push + cross-GPU barrier (or flagged packets),
+    grid-wide barrier, routing, grid-wide barrier, tcgen05 GEMM that gathers token rows from the
+    buffer the peers just filled.  Built from the three stand-alone plans."""
+
+    def __init__(self, heap: SymmetricHeap, agv, route: RoutePlan, fc1: GroupedGemmPlan, grid: int = NUM_SMS):
+        if fc1.mode != _ext.GEMM_FC1:
+            raise ValueError("DispatchRouteFc1Plan needs an FC1 plan")
+        if not (1 <= grid <= NUM_SMS):
+            raise ValueError("the fused kernel needs all its blocks resident at once: grid <= number of SMs")
+        self.heap, self.agv, self.route, self.fc1, self.grid = heap, agv, route, fc1, grid
+
+    def launch(self, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        _ext.check(lib.mcb_launch_dispatch_route_fc1(C.c_void_p(self.fc1.tmap[1]), C.byref(self.fc1.args),
+                                                     C.byref(self.heap.ctx()), C.byref(self.agv.args),
+                                                     C.byref(self.route.args), self.grid, int(pdl),
+                                                     _ext.stream_handle(stream)), "dispatch_route_fc1")

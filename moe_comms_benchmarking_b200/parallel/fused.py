@@ -11,7 +11,9 @@ expert computation the transport exists for.  Per layer and rank:
     FC2        y = prob * (act Wd^T)                              csrc/gemm.cu    grouped_gemm_kernel<FC2>
     combine    out[t] = sum_ranks sum_local-pairs y               csrc/route.cu   combine_kernel
 
-By default FC2 and the combine are ONE kernel (``fc2_combine_kernel`` in csrc/gemm.cu: the GEMM
+By default the layer is TWO kernels.  Dispatch, routing and FC1 are one
+(``dispatch_route_fc1_kernel``: multicast push + cross-GPU barrier, grid barrier, routing, grid
+barrier, GEMM; ``fuse_dispatch=False`` launches the three separately), and FC2 and the combine are one (``fc2_combine_kernel`` in csrc/gemm.cu: the GEMM
 CTAs finish their tiles, meet in a grid-wide barrier and run the combine, multimem.ld_reduce
 included); ``fuse_combine=False`` launches them separately.
 
@@ -27,7 +29,7 @@ import torch.distributed as dist
 from ..config import Config
 from ..ops import _ext, oracle
 from ..ops.dense import AllGatherVPlan, MetadataPlan, DEFAULT_GRID, DEFAULT_THREADS, agv_ll_stage_bytes
-from ..ops.experts import (ExpertCombinePlan, ExpertWeights, Fc2CombinePlan, GroupedGemmPlan, RouteBuffers, RoutePlan,
+from ..ops.experts import (DispatchRouteFc1Plan, ExpertCombinePlan, ExpertWeights, Fc2CombinePlan, GroupedGemmPlan, RouteBuffers, RoutePlan,
                            NUM_SMS)
 from .base import Dispatcher
 from .dense import resolve_ll_rows
@@ -40,7 +42,7 @@ class FusedExpertDispatcher(Dispatcher):
     def __init__(self, cfg: Config, group, heap: SymmetricHeap | None = None, num_sms: int = DEFAULT_GRID,
                  threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto", ll_rows: int = -1,
                  num_layers: int = 88, weight_budget_gb: float = 64.0, weight_seed: int = 7,
-                 fuse_combine: bool = True, coop_pdl: bool = False, device=None):
+                 fuse_combine: bool = True, fuse_dispatch: bool = True, coop_pdl: bool = False, device=None):
         super().__init__(cfg, group, device)
         self.heap, self._own_heap = heap, heap is None
         self.num_sms, self.threads, self.pdl, self.transport = int(num_sms), int(threads), bool(pdl), transport
@@ -48,7 +50,8 @@ class FusedExpertDispatcher(Dispatcher):
         self.num_layers, self.weight_budget_gb, self.weight_seed = num_layers, weight_budget_gb, weight_seed
         self.fuse_combine = bool(fuse_combine)
         self.coop_pdl = bool(coop_pdl)   # cooperative + programmatic dependent launch on the fused kernel
-        self.kernel_launches_per_step = lambda nl: 1 + (4 if self.fuse_combine else 5) * nl
+        self.fuse_dispatch = bool(fuse_dispatch)
+        self.kernel_launches_per_step = lambda nl: 1 + (5 - int(self.fuse_combine) - 2 * int(self.fuse_dispatch)) * nl
 
     @staticmethod
     def heap_specs(cfg: Config, ll_rows: int = -1):
@@ -100,6 +103,7 @@ class FusedExpertDispatcher(Dispatcher):
         self.combine_plan = ExpertCombinePlan(h, self.y, self.route, self.partial, self.out_buf, self.n_local,
                                               self.step_metadata, cap, grid=NUM_SMS)
         self.fc2_combine = [Fc2CombinePlan(h, f, self.combine_plan) for f in self.fc2]
+        self.dispatch_fc1 = [DispatchRouteFc1Plan(h, self.agv_plan, self.route_plan, f) for f in self.fc1]
         torch.cuda.synchronize()
         dist.barrier(self.group)
         self._built = True
@@ -135,14 +139,17 @@ class FusedExpertDispatcher(Dispatcher):
         self.combine_plan.launch(self.pdl)
 
     def layer(self, layer: int = 0):
-        self.dispatch()
-        if self.fuse_combine:
-            s = layer % len(self.weights)
+        s = layer % len(self.weights)
+        if self.fuse_dispatch:
+            self.dispatch_fc1[s].launch(self.pdl and self.coop_pdl)
+        else:
+            self.dispatch()
             self.route_plan.launch(self.pdl)
             self.fc1[s].launch(self.pdl)
+        if self.fuse_combine:
             self.fc2_combine[s].launch(self.pdl and self.coop_pdl)
         else:
-            self.experts(layer)
+            self.fc2[s].launch(self.pdl)
             self.combine()
 
     def step(self):

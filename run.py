@@ -71,6 +71,10 @@ def parse_args(argv=None):
                    help="dense dispatcher: steps with at most this many tokens over all ranks use "
                         "low-latency flagged packets instead of barrier + multicast (0 = never, -1 = measured default)")
     p.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch")
+    p.add_argument("--coop-pdl", action="store_true",
+                   help="fused: also allow programmatic dependent launch on the cooperative fused kernels")
+    p.add_argument("--no-fuse-dispatch", action="store_true",
+                   help="fused: launch dispatch, routing and the FC1 GEMM as three kernels instead of one")
     p.add_argument("--no-fuse-combine", action="store_true",
                    help="fused: launch the FC2 GEMM and the combine as two kernels instead of one")
     p.add_argument("--weight-budget-gb", type=float, default=48.0,
@@ -124,7 +128,8 @@ def build_dispatchers(names, cfg, group, args, device, sms_list):
             out.append(FusedExpertDispatcher(cfg, group, heap, pdl=not args.no_pdl, ll_rows=args.ll_rows,
                                              num_layers=1 if args.validate else (args.num_layers or 88),
                                              weight_budget_gb=args.weight_budget_gb,
-                                             fuse_combine=not args.no_fuse_combine))
+                                             fuse_combine=not args.no_fuse_combine,
+                                             fuse_dispatch=not args.no_fuse_dispatch, coop_pdl=args.coop_pdl))
         elif n == "nccl":
             from moe_comms_benchmarking_b200.parallel.nccl import NCCLDispatcher
             out.append(NCCLDispatcher(cfg, group))

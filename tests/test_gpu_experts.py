@@ -82,14 +82,14 @@ def test_route_fc1_fc2_combine_against_oracle(world1, T, E, K, H, I):
         assert float((out[:T].float().cpu() - ref).abs().max()) < 0.03 * s + 1e-3, "layer"
 
 
-@pytest.mark.parametrize("fuse", [True, False])
-def test_fused_dispatcher_world1(world1, fuse):
+@pytest.mark.parametrize("fuse,fuse_d", [(True, True), (False, False), (True, False), (False, True)])
+def test_fused_dispatcher_world1(world1, fuse, fuse_d):
     from moe_comms_benchmarking_b200.config import Config
     from moe_comms_benchmarking_b200.parallel.fused import FusedExpertDispatcher
     from moe_comms_benchmarking_b200.utils.inputs import make_inputs
     from moe_comms_benchmarking_b200.utils.timing import capture_graph
     cfg = Config(num_experts=16, topk=4, hidden=512, intermediate=256, ep_size=1, per_rank_cap=160)
-    d = FusedExpertDispatcher(cfg, world1, num_layers=3, weight_budget_gb=1.0, fuse_combine=fuse)
+    d = FusedExpertDispatcher(cfg, world1, num_layers=3, weight_budget_gb=1.0, fuse_combine=fuse, fuse_dispatch=fuse_d)
     d.build()
     for name, ok, detail in d.validate():
         assert ok, f"{name}: {detail}"
