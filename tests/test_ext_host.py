@@ -117,3 +117,47 @@ def test_a2a_and_norm_plans_validate_arguments():
     RsAddNormAgPlan(h, buf, torch.zeros(8, 64, dtype=torch.bfloat16), torch.ones(64, dtype=torch.bfloat16))
     with pytest.raises(ValueError):
         RsAddNormAgPlan(h, buf, torch.zeros(4, 64, dtype=torch.bfloat16), torch.ones(64, dtype=torch.bfloat16))
+
+
+def test_expert_plans_validate_arguments(lib):
+    from moe_comms_benchmarking_b200.ops.experts import (DispatchRouteFc1Plan, ExpertCombinePlan, Fc2CombinePlan,
+                                                         GroupedGemmPlan, RouteBuffers, RoutePlan)
+    h = _heap(8 << 20)
+    T, K, E, H, I = 16, 4, 8, 256, 128
+    route = RouteBuffers(T, K, E, "cpu")
+    assert route.max_pairs == T * 4 and route.max_tiles == E + route.max_pairs // 128 + 1
+    idx = torch.zeros(T, K, dtype=torch.int64)
+    ntok = torch.zeros(1, dtype=torch.int32)
+    rp = RoutePlan(route, idx, None, ntok, expert_begin=0)
+    with pytest.raises(ValueError):
+        RoutePlan(route, idx.int(), None, ntok, expert_begin=0)
+    with pytest.raises(ValueError):
+        RoutePlan(route, idx, None, ntok, expert_begin=0, grid=500)
+    x = torch.zeros(T, H, dtype=torch.bfloat16)
+    act = torch.zeros(route.max_pairs, I, dtype=torch.bfloat16)
+    y = torch.zeros(route.max_pairs, H, dtype=torch.bfloat16)
+    tmap = (None, 0)            # plans only store the tensor-map handle
+    fc1 = GroupedGemmPlan(_ext.GEMM_FC1, tmap, route, x, act, 2 * I, H)
+    fc2 = GroupedGemmPlan(_ext.GEMM_FC2, tmap, route, act, y, H, I)
+    with pytest.raises(ValueError):      # A rows do not match k_total
+        GroupedGemmPlan(_ext.GEMM_FC1, tmap, route, x, act, 2 * I, H * 2)
+    with pytest.raises(ValueError):      # out has the wrong width
+        GroupedGemmPlan(_ext.GEMM_FC2, tmap, route, act, act, H, I)
+    with pytest.raises(ValueError):      # k_total not a multiple of 64
+        GroupedGemmPlan(_ext.GEMM_FC2, tmap, route, torch.zeros(route.max_pairs, 96, dtype=torch.bfloat16), y, H, 96)
+    partial = h.alloc("partial", [T, H], torch.bfloat16)
+    meta = torch.zeros(4, dtype=torch.int32)
+    out = torch.zeros(T, H, dtype=torch.bfloat16)
+    comb = ExpertCombinePlan(h, y, route, partial, out, ntok, meta, T)
+    with pytest.raises(ValueError):      # partial buffer smaller than the capacity
+        ExpertCombinePlan(h, y, route, partial, out, ntok, meta, T * 2)
+    Fc2CombinePlan(h, fc2, comb)
+    with pytest.raises(ValueError):
+        Fc2CombinePlan(h, fc1, comb)
+    with pytest.raises(ValueError):      # all blocks must be resident at once
+        Fc2CombinePlan(h, fc2, comb, grid=149)
+    gh = h.alloc("gh2", [T, H], torch.bfloat16)
+    agv = AllGatherVPlan(h, [gh], [x], ntok, meta, T)
+    DispatchRouteFc1Plan(h, agv, rp, fc1)
+    with pytest.raises(ValueError):
+        DispatchRouteFc1Plan(h, agv, rp, fc2)
