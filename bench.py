@@ -106,10 +106,11 @@ def run_native(args):
         eng.check_health()
         return ms, (h, i, w)
 
+    # clocks and throttle reasons are sampled while the timed regions run (sweep + headline + e2e)
+    sampler = ClockSampler(local_rank, period_ms=50).start() if rank == 0 else None
     sweep_ms = {}
     for b in sweep:
         sweep_ms[str(b)], _ = measure(b, max(3, args.steps // 2), max(3, args.warmup // 2))
-    sampler = ClockSampler(local_rank).start() if rank == 0 else None
     value_ms, (h, i, w) = measure(B, args.steps, args.warmup)
     # end to end: pinned host inputs in, combined output out, every step
     hp, ip, wp = pinned_inputs(h, i, w)
