@@ -145,8 +145,6 @@ class A2ADispatcher(Dispatcher):
             idx = (torch.stack([torch.randperm(E, generator=gen, device=dev)[:K] for _ in range(n)])
                    if n else torch.empty(0, K, dtype=torch.int64, device=dev))
             got = self.functional_roundtrip(x, idx).float()
-            # every rank also checks what it RECEIVED: row counts per source
-            expect_counts = None
             if n:
                 m = torch.tensor([torch.unique(idx[t] // epr).numel() for t in range(n)], device=dev,
                                  dtype=torch.float32).view(n, 1)
@@ -157,7 +155,6 @@ class A2ADispatcher(Dispatcher):
                 detail = f"n={n} max|got-m*x|={err:.4f} ({100 * err / scale:.2f}% of {scale:.2f})"
             else:
                 ok, detail = True, "n=0 (idle rank still takes part in dispatch and combine)"
-            del expect_counts
             results.append((f"{self.name} dispatch->combine B={B:<4d}", bool(ok), detail))
         try:
             self.check_health()

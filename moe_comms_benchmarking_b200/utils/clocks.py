@@ -2,6 +2,7 @@
 region runs.  Read-only: nothing here changes a GPU setting."""
 from __future__ import annotations
 
+import os
 import shutil
 import statistics
 import subprocess
@@ -39,7 +40,13 @@ class ClockSampler:
             self._proc.kill()
         self._file.flush()
         self._file.seek(0)
-        return parse_samples(self._file.read())
+        text = self._file.read()
+        self._file.close()
+        try:
+            os.unlink(self._file.name)
+        except OSError:
+            pass
+        return parse_samples(text)
 
 
 def parse_samples(text: str) -> dict:
