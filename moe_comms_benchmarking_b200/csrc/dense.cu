@@ -138,7 +138,7 @@ __device__ __forceinline__ uint4 p2p_reduce_pack(const McbCtx& c, uint64_t off) 
 
 // Low-latency reduce-scatter-V (bf16): push every valid row of my partial sums to its owner as
 // packets, then sum, for each of my own rows, the packets of all ranks in rank order (fp32).
-__device__ __noinline__ void rsv_ll(const McbCtx& c, const McbRsvArgs& a, int n, int offset, int valid,
+__device__ __forceinline__ void rsv_ll(const McbCtx& c, const McbRsvArgs& a, int n, int offset, int valid,
                                        uint32_t flag, const int* s_prefix) {
   const int wpr = (int)(a.row_bytes >> 3);
   const uint64_t per_src = (uint64_t)a.ll_src_rows * wpr * 16;
@@ -195,21 +195,21 @@ __device__ __noinline__ void rsv_ll(const McbCtx& c, const McbRsvArgs& a, int n,
 }
 
 template <bool EMU>
-__global__ void __launch_bounds__(512, 2) rsv_kernel(const __grid_constant__ McbCtx ctx_p,
+__global__ void __launch_bounds__(512) rsv_kernel(const __grid_constant__ McbCtx ctx_p,
                                                    const __grid_constant__ McbRsvArgs args_p,
                                                    const McbCtx* ectx, const McbRsvArgs* eargs) {
   const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
   const McbRsvArgs& a = EMU ? eargs[blockIdx.y] : args_p;
   const int bid = blockIdx.x;
-  int n = 0, valid_pre = 0, offset = 0, ep_max = 0;
+  int n = 0, valid_pre = 0, offset = 0, ep_max = 0, meta_epoch = 0;
   if (a.meta_stable) {
     n = *a.n_local;
-    valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2];
+    valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2]; meta_epoch = a.step_meta[3];
   }
   pdl_wait();
   if (!a.meta_stable) {
     n = *a.n_local;
-    valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2];
+    valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2]; meta_epoch = a.step_meta[3];
   }
   const int nact = active_blocks((int)gridDim.x, ep_max, a.row_bytes, (int)blockDim.x);
   pdl_launch_dependents();
@@ -223,14 +223,20 @@ __global__ void __launch_bounds__(512, 2) rsv_kernel(const __grid_constant__ Mcb
         if (threadIdx.x == 0) report_error(c, MCB_ERR_BOUNDS, (uint32_t)a.site, (uint32_t)bid, (uint32_t)n, (uint32_t)valid);
         return;
       }
-      // Row ownership: prefix sums of the per-rank counts published by the metadata kernel.
-      if (threadIdx.x == 0) {
-        const uint32_t par = ((uint32_t)a.step_meta[3] - 1u) & 1u;
+      // Row ownership: prefix sums of the per-rank counts published by the metadata kernel.  The
+      // counts are read by one thread each (independent loads), then summed from shared memory.
+      {
+        const uint32_t par = ((uint32_t)meta_epoch - 1u) & 1u;
         const uint8_t* counts = c.heap_local + a.counts_off + (uint64_t)par * MCB_MAX_RANKS * 4;
+        for (int p = threadIdx.x; p < c.world; p += blockDim.x) s_prefix[p + 1] = (int)ld_relaxed_sys(counts + p * 4);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
         int run = 0;
         for (int p = 0; p < c.world; ++p) {
+          const int cnt = s_prefix[p + 1];
           s_prefix[p] = run;
-          run += (int)ld_relaxed_sys(counts + p * 4);
+          run += cnt;
         }
         s_prefix[c.world] = run;
       }

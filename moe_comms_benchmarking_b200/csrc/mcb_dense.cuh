@@ -124,7 +124,7 @@ __device__ __forceinline__ bool agv_ll_eligible(const McbCtx& c, const McbAgvArg
 
 // Low-latency all-gather-V: send my rows as packets to every rank's staging area, then poll my
 // own staging area for all `valid` rows and unpack them into the gathered tensors.
-static __device__ __noinline__ void agv_ll(const McbCtx& c, const McbAgvArgs& a, int n, int offset, int valid,
+__device__ __forceinline__ void agv_ll(const McbCtx& c, const McbAgvArgs& a, int n, int offset, int valid,
                                        uint32_t flag) {
   int w[MCB_MAX_TENSORS];
   int wpr = 0;
