@@ -26,12 +26,12 @@ from .symm_heap import SymmetricHeap, required_bytes
 
 
 def resolve_ll_rows(cfg: Config, ll_rows: int) -> int:
-    """Row limit of the low-latency packet mode.  ``-1`` picks the measured crossover with the
-    barrier + multicast mode on 8xB200 (about 256 rows at EP=8, 512 at EP=2): min(512, 2048 / EP)."""
+    """Row limit of the low-latency packet mode.  ``-1`` picks 256 rows, the measured crossover
+    with the barrier + multicast mode on B200 (256 at EP=8, between 256 and 512 at EP=2 and EP=4)."""
     if cfg.ep_size <= 1:
         return 0
     if ll_rows < 0:
-        ll_rows = min(512, 2048 // cfg.ep_size)
+        ll_rows = 256
     return min(int(ll_rows), max(cfg.global_cap, 1))
 
 
