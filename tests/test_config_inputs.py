@@ -86,3 +86,22 @@ def test_size_mb():
     assert size_mb([1], torch.int32) == 1
     assert size_mb([1024, 1024], torch.bfloat16) == 2
     assert size_mb([1024, 1025], torch.bfloat16) == 3
+
+
+def test_low_latency_limit_and_heap_sizing():
+    from moe_comms_benchmarking_b200.ops.dense import agv_ll_stage_bytes, rsv_ll_stage_bytes
+    from moe_comms_benchmarking_b200.parallel.dense import DenseDispatcher, resolve_ll_rows
+    from moe_comms_benchmarking_b200.parallel.symm_heap import required_bytes
+    assert resolve_ll_rows(Config(ep_size=1, per_rank_cap=64), -1) == 0           # nobody to talk to
+    assert resolve_ll_rows(Config(ep_size=8, per_rank_cap=1024), -1) == 256
+    assert resolve_ll_rows(Config(ep_size=8, per_rank_cap=4), -1) == 32           # never above the capacity
+    assert resolve_ll_rows(Config(ep_size=2, per_rank_cap=4096), 100) == 100
+    assert resolve_ll_rows(Config(ep_size=2, per_rank_cap=4096), 0) == 0
+    # one 16-byte packet per 8 bytes of row, two parities
+    assert agv_ll_stage_bytes(256, [2048, 176, 88]) == 2 * 256 * 289 * 16
+    assert rsv_ll_stage_bytes(8, 256, 1024, 2048) == 2 * 8 * 256 * 256 * 16
+    assert rsv_ll_stage_bytes(8, 256, 64, 2048) == 2 * 8 * 64 * 256 * 16
+    cfg = Config(ep_size=8, per_rank_cap=1024)
+    specs = DenseDispatcher.heap_specs(cfg)
+    assert specs[0][0] == [8192, 1024] and len(specs) == 6
+    assert required_bytes(specs) > 8192 * (2048 + 176 + 88 + 2048)
