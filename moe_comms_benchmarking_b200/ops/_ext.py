@@ -144,8 +144,14 @@ def load():
     if _lib is not None:
         return _lib
     if not LIB_PATH.exists():
-        raise ExtensionMissing(
-            f"{LIB_PATH} is missing: build it with `python -m moe_comms_benchmarking_b200.build`")
+        # Build in place when the toolkit is there; otherwise fail loudly (there is no fallback path).
+        try:
+            from .. import build as _build
+            _build.build()
+        except Exception as e:
+            raise ExtensionMissing(
+                f"{LIB_PATH} is missing and could not be built ({type(e).__name__}: {e}); "
+                f"run `python -m moe_comms_benchmarking_b200.build`") from e
     lib = C.CDLL(os.fspath(LIB_PATH))
     for name, struct in _STRUCTS.items():
         fn = getattr(lib, f"mcb_sizeof_{name}")
