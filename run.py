@@ -35,6 +35,7 @@ from moe_comms_benchmarking_b200.models.presets import PRESETS, get_preset  # no
 from moe_comms_benchmarking_b200.parallel.dist import init_distributed  # noqa: E402
 from moe_comms_benchmarking_b200.utils.inputs import make_inputs, rank_counts  # noqa: E402
 from moe_comms_benchmarking_b200.utils.report import CsvSink, Row, STDOUT_HEADER  # noqa: E402
+from moe_comms_benchmarking_b200.utils.trace import phase  # noqa: E402
 
 IMPL_CHOICES = ["deepep", "nvls", "nccl", "both", "all", "dense", "a2a", "fused", "gloo"]
 
@@ -200,11 +201,12 @@ def main(argv=None) -> int:
         say(f"# impl={args.impl} -> {'+'.join(names)} num_layers={nl} device_sms={dev_sms} "
             f"num_sms_sweep={sms_sweep} routing={cfg.routing} counts={cfg.counts} dispatch={args.dispatch_dtype}")
 
-    benchers, heap = build_dispatchers(names, cfg, group, args, device, sms_sweep)
-    dist.barrier(group)
-    for b in benchers:
-        b.build()
-    dist.barrier(group)
+    with phase("build", rank):
+        benchers, heap = build_dispatchers(names, cfg, group, args, device, sms_sweep)
+        dist.barrier(group)
+        for b in benchers:
+            b.build()
+        dist.barrier(group)
     if rank == 0 and heap is not None:
         say(f"# symmetric heap: {heap.bytes_used() / 2**20:.1f} MiB used, transport={heap.transport}")
 
@@ -246,8 +248,9 @@ def main(argv=None) -> int:
                 hidden, topk_idx, topk_w = make_inputs(cfg, B, device, n=counts[rank])
                 b.setup_batch(hidden, topk_idx, topk_w)
                 if on_gpu:
-                    (_, step_us), used_graph = timed_with_fallback(lambda: b.decode_step(nl), group, args.warmup,
-                                                                   args.reps, args.timing, rank)
+                    with phase(f"time {b.name} B={B}", rank):
+                        (_, step_us), used_graph = timed_with_fallback(lambda: b.decode_step(nl), group, args.warmup,
+                                                                       args.reps, args.timing, rank)
                     b.check_health()
                 else:
                     import time

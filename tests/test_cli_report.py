@@ -68,3 +68,17 @@ def test_plot_loader_and_ticks(tmp_path, capsys):
     assert plot.main(["--csv", path, "--out", str(tmp_path / "o.png")]) == 0
     out = capsys.readouterr().out
     assert "wrote" in out or "787.030" in out
+
+
+def test_phase_tracing(monkeypatch, capsys):
+    from moe_comms_benchmarking_b200.utils import trace
+    trace.clear()
+    monkeypatch.setenv("MCB_TRACE", "1")
+    with trace.phase("unit-test phase"):
+        pass
+    assert trace.records()[-1][0] == "unit-test phase" and trace.records()[-1][1] >= 0
+    assert "# [trace] unit-test phase:" in capsys.readouterr().out
+    monkeypatch.setenv("MCB_TRACE", "0")
+    with trace.phase("quiet"):
+        pass
+    assert "quiet" not in capsys.readouterr().out
