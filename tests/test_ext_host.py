@@ -161,3 +161,20 @@ def test_expert_plans_validate_arguments(lib):
     DispatchRouteFc1Plan(h, agv, rp, fc1)
     with pytest.raises(ValueError):
         DispatchRouteFc1Plan(h, agv, rp, fc2)
+
+
+def test_capability_checks():
+    from moe_comms_benchmarking_b200 import ops
+    assert not ops.is_device_multimem_capable("cpu") and not ops.is_device_tcgen05_capable("cpu")
+    h = _heap(1 << 16)
+    assert not ops.heap_has_multicast(h)
+    assert ops.row_access_bytes(torch.zeros(4, 1024, dtype=torch.bfloat16)) == 16
+    assert ops.row_access_bytes(torch.zeros(4, 22, dtype=torch.float32)) == 8      # 88-byte rows
+    assert ops.row_access_bytes(torch.zeros(4, 3, dtype=torch.float32)) == 4
+    assert ops.row_access_bytes(torch.zeros(4, 3, dtype=torch.uint8)) == 0
+    assert ops.row_access_bytes(torch.zeros(4, 8, dtype=torch.float32).t()) == 0   # not contiguous
+    assert ops.are_tensors_gather_eligible(torch.zeros(2, 22, dtype=torch.int64), torch.zeros(2, 22))
+    assert not ops.are_tensors_gather_eligible()
+    assert ops.are_tensors_reduce_eligible(torch.zeros(2, 1024, dtype=torch.bfloat16))
+    assert not ops.are_tensors_reduce_eligible(torch.zeros(2, 22))                 # 88-byte rows
+    assert not ops.are_tensors_reduce_eligible(torch.zeros(2, 8, dtype=torch.int32))
