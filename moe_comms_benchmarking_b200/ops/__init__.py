@@ -14,11 +14,25 @@ their counterparts here:
     (no counterpart)                 -> RoutePlan, GroupedGemmPlan, ExpertCombinePlan,
                                         DispatchRouteFc1Plan, Fc2CombinePlan
 """
-from .a2a import A2ABuffers, A2ACombinePlan, A2ADispatchPlan, a2a_decode_step  # noqa: F401
-from .capability import (are_tensors_gather_eligible, are_tensors_reduce_eligible, heap_has_multicast,  # noqa: F401
-                         is_device_multimem_capable, is_device_tcgen05_capable, row_access_bytes)
-from .dense import (AllGatherVPlan, MetadataPlan, ReduceScatterVPlan, UniformAllGatherPlan,  # noqa: F401
-                    UniformReduceScatterPlan, dense_decode_step)
-from .experts import (DispatchRouteFc1Plan, ExpertCombinePlan, ExpertWeights, Fc2CombinePlan,  # noqa: F401
-                      GroupedGemmPlan, RouteBuffers, RoutePlan)
-from .norm import RsAddNormAgPlan  # noqa: F401
+import importlib
+
+# Resolved on first use: the plan modules import the symmetric heap, which imports ``ops._ext``;
+# importing them here eagerly would close that loop.
+_EXPORTS = {
+    "a2a": ["A2ABuffers", "A2ACombinePlan", "A2ADispatchPlan", "a2a_decode_step"],
+    "capability": ["are_tensors_gather_eligible", "are_tensors_reduce_eligible", "heap_has_multicast",
+                   "is_device_multimem_capable", "is_device_tcgen05_capable", "row_access_bytes"],
+    "dense": ["AllGatherVPlan", "MetadataPlan", "ReduceScatterVPlan", "UniformAllGatherPlan",
+              "UniformReduceScatterPlan", "dense_decode_step"],
+    "experts": ["DispatchRouteFc1Plan", "ExpertCombinePlan", "ExpertWeights", "Fc2CombinePlan", "GroupedGemmPlan",
+                "RouteBuffers", "RoutePlan"],
+    "norm": ["RsAddNormAgPlan"],
+}
+_WHERE = {name: mod for mod, names in _EXPORTS.items() for name in names}
+__all__ = sorted(_WHERE)
+
+
+def __getattr__(name):
+    if name in _WHERE:
+        return getattr(importlib.import_module(f"{__name__}.{_WHERE[name]}"), name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
