@@ -8,7 +8,8 @@
 Same inputs and outputs as the reference's plot_results.py (CSV schema run.py:233-238; log2 x
 axis with 1k/128k/1M tick labels, log y axis, last point annotated with %.2f ms, EP inferred
 from the length of per_rank_counts).  matplotlib (Agg) is optional: without it the script
-prints the table it would have drawn and writes no image; the CSV is the artefact of record.
+prints the table and draws the same chart itself as an SVG file (``--out`` with its extension
+replaced by ``.svg``), so a machine without matplotlib still gets an image.
 """
 from __future__ import annotations
 
@@ -76,6 +77,67 @@ def text_table(rows) -> str:
     return "\n".join(lines)
 
 
+SVG_COLORS = {"tab:blue": "#1f77b4", "tab:cyan": "#17becf", "tab:orange": "#ff7f0e", "tab:green": "#2ca02c",
+              "tab:red": "#d62728", "gray": "#7f7f7f"}
+
+
+def render_svg(rows, title, xlabel="global batch size B  (decode tokens across all EP ranks)") -> str:
+    """Latency-vs-B chart as a stand-alone SVG: log2 x axis with 1k/128k/1M ticks, log10 y axis,
+    one line per implementation, last point annotated with %.2f ms."""
+    import math
+    ser = series_vs_b(rows)
+    if not ser:
+        return "<svg xmlns='http://www.w3.org/2000/svg' width='10' height='10'/>"
+    W, H, L, R, T, B = 860, 540, 70, 150, 60, 60
+    xs = sorted({b for pts in ser.values() for b, _ in pts})
+    ys = [y for pts in ser.values() for _, y in pts if y > 0]
+    x0, x1 = math.log2(xs[0]), math.log2(xs[-1]) if xs[-1] > xs[0] else math.log2(xs[0]) + 1
+    y0, y1 = math.floor(math.log10(min(ys))), math.ceil(math.log10(max(ys)))
+    if y1 == y0:
+        y1 += 1
+
+    def px(b):
+        return L + (math.log2(b) - x0) / (x1 - x0) * (W - L - R)
+
+    def py(v):
+        return H - B - (math.log10(v) - y0) / (y1 - y0) * (H - T - B)
+
+    out = [f"<svg xmlns='http://www.w3.org/2000/svg' width='{W}' height='{H}' font-family='sans-serif' font-size='11'>",
+           f"<rect width='{W}' height='{H}' fill='white'/>"]
+    for i, line in enumerate(title.split("\n")):
+        out.append(f"<text x='{W / 2}' y='{22 + 15 * i}' text-anchor='middle' font-size='12'>{line}</text>")
+    for e in range(y0, y1 + 1):
+        y = py(10.0 ** e)
+        out.append(f"<line x1='{L}' y1='{y:.1f}' x2='{W - R}' y2='{y:.1f}' stroke='#cccccc'/>")
+        out.append(f"<text x='{L - 6}' y='{y + 4:.1f}' text-anchor='end'>{10.0 ** e:g}</text>")
+        for m in range(2, 10):
+            if e < y1:
+                ym = py(m * 10.0 ** e)
+                out.append(f"<line x1='{L}' y1='{ym:.1f}' x2='{W - R}' y2='{ym:.1f}' stroke='#eeeeee'/>")
+    for b in xs:
+        x = px(b)
+        out.append(f"<line x1='{x:.1f}' y1='{T}' x2='{x:.1f}' y2='{H - B}' stroke='#eeeeee'/>")
+        out.append(f"<text x='{x:.1f}' y='{H - B + 15}' text-anchor='middle'>{ktick(b)}</text>")
+    out.append(f"<rect x='{L}' y='{T}' width='{W - L - R}' height='{H - T - B}' fill='none' stroke='black'/>")
+    out.append(f"<text x='{(L + W - R) / 2}' y='{H - 18}' text-anchor='middle'>{xlabel}</text>")
+    out.append(f"<text x='16' y='{(T + H - B) / 2}' text-anchor='middle' transform='rotate(-90 16 {(T + H - B) / 2})'>"
+               "latency per decode step (ms)</text>")
+    for i, (impl, pts) in enumerate(ser.items()):
+        col = SVG_COLORS.get(IMPL_COLOR.get(impl, "gray"), "#7f7f7f")
+        path = " ".join(f"{px(b):.1f},{py(v):.1f}" for b, v in pts if v > 0)
+        out.append(f"<polyline points='{path}' fill='none' stroke='{col}' stroke-width='2'/>")
+        for b, v in pts:
+            if v > 0:
+                out.append(f"<circle cx='{px(b):.1f}' cy='{py(v):.1f}' r='3' fill='{col}'/>")
+        lb, lv = pts[-1]
+        out.append(f"<text x='{px(lb) + 6:.1f}' y='{py(lv) + 4:.1f}' fill='{col}' font-size='10'>{lv:.2f}</text>")
+        ly = T + 14 + 16 * i
+        out.append(f"<line x1='{W - R + 40}' y1='{ly - 4}' x2='{W - R + 60}' y2='{ly - 4}' stroke='{col}' stroke-width='2'/>")
+        out.append(f"<text x='{W - R + 64}' y='{ly}' font-size='9'>{IMPL_NAME.get(impl, impl)[:18]}</text>")
+    out.append("</svg>")
+    return "\n".join(out)
+
+
 def main(argv=None):
     p = argparse.ArgumentParser()
     p.add_argument("--csv", default="results.csv")
@@ -92,8 +154,15 @@ def main(argv=None):
         import matplotlib.pyplot as plt
         from matplotlib import cm
     except ImportError:
-        print("matplotlib is not installed; table instead of an image (ms per decode step):")
+        print("matplotlib is not installed; table (ms per decode step) and a self-drawn SVG instead:")
         print(text_table(rows))
+        if args.x == "B" and rows:
+            svg_path = (args.out[:-4] if args.out.lower().endswith(".png") else args.out) + ".svg"
+            title = args.title or (f"MoE decode dispatch+combine latency — {args.num_layers} MoE layers/step\n"
+                                   f"{subtitle(ep)}")
+            with open(svg_path, "w") as f:
+                f.write(render_svg(rows, title))
+            print(f"wrote {svg_path}")
         return 0
     fig, ax = plt.subplots(figsize=(8.5, 5.5))
     if args.x == "num_sms":

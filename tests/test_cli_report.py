@@ -67,7 +67,13 @@ def test_plot_loader_and_ticks(tmp_path, capsys):
     assert "EP=4" in plot.subtitle(4)
     assert plot.main(["--csv", path, "--out", str(tmp_path / "o.png")]) == 0
     out = capsys.readouterr().out
-    assert "wrote" in out or "787.030" in out
+    assert "wrote" in out
+    svg = plot.render_svg(rows, "title line 1\ntitle line 2")
+    import xml.dom.minidom
+    doc = xml.dom.minidom.parseString(svg)
+    assert len(doc.getElementsByTagName("polyline")) == 1          # one implementation
+    texts = [t.firstChild.data for t in doc.getElementsByTagName("text") if t.firstChild]
+    assert "1k" in texts and "1M" in texts and "787.03" in texts    # tick labels and last-point annotation
 
 
 def test_phase_tracing(monkeypatch, capsys):
