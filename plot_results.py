@@ -19,7 +19,7 @@ import statistics
 import sys
 
 IMPL_NAME = {"a2a": "A2A-V (peer ld/st)", "a2a-fp8": "A2A-V e4m3 dispatch", "dense": "dense AGV/RSV (multimem)",
-             "nccl": "NCCL (AllGather/ReduceScatter)", "deepep": "DeepEP-v2 (A2A)", "nvls": "NVLS (AGv/RSv)",
+             "nccl": "NCCL AllGather/RS", "deepep": "DeepEP-v2 (A2A)", "nvls": "reference NVLS (Triton)",
              "fused": "fused experts (tcgen05)"}
 IMPL_COLOR = {"a2a": "tab:blue", "a2a-fp8": "tab:cyan", "dense": "tab:orange", "nccl": "tab:green",
               "deepep": "tab:blue", "nvls": "tab:orange", "fused": "tab:red"}
@@ -133,7 +133,7 @@ def render_svg(rows, title, xlabel="global batch size B  (decode tokens across a
         out.append(f"<text x='{px(lb) + 6:.1f}' y='{py(lv) + 4:.1f}' fill='{col}' font-size='10'>{lv:.2f}</text>")
         ly = T + 14 + 16 * i
         out.append(f"<line x1='{W - R + 40}' y1='{ly - 4}' x2='{W - R + 60}' y2='{ly - 4}' stroke='{col}' stroke-width='2'/>")
-        out.append(f"<text x='{W - R + 64}' y='{ly}' font-size='9'>{IMPL_NAME.get(impl, impl)[:18]}</text>")
+        out.append(f"<text x='{W - R + 64}' y='{ly}' font-size='9'>{IMPL_NAME.get(impl, impl)[:26]}</text>")
     out.append("</svg>")
     return "\n".join(out)
 
