@@ -22,7 +22,7 @@ IMPL_NAME = {"a2a": "A2A-V (peer ld/st)", "a2a-fp8": "A2A-V e4m3 dispatch", "den
              "nccl": "NCCL AllGather/RS", "deepep": "DeepEP-v2 (A2A)", "nvls": "reference NVLS (Triton)",
              "fused": "fused experts (tcgen05)"}
 IMPL_COLOR = {"a2a": "tab:blue", "a2a-fp8": "tab:cyan", "dense": "tab:orange", "nccl": "tab:green",
-              "deepep": "tab:blue", "nvls": "tab:orange", "fused": "tab:red"}
+              "deepep": "tab:blue", "nvls": "tab:red", "fused": "tab:cyan"}
 
 
 def load(path):
