@@ -47,6 +47,9 @@ def parse_args(argv=None):
     p.add_argument("--sweep", default="1,64,512,4096", help="extra global batches reported under 'sweep'")
     p.add_argument("--no-pdl", action="store_true")
     p.add_argument("--ll-rows", type=int, default=-1)
+    p.add_argument("--groups", type=int, default=-1, help="pipeline groups of the persistent dense step kernel "
+                                                          "(-1 = the dispatcher's default)")
+    p.add_argument("--no-persistent", action="store_true", help="one kernel per operation instead of one per step")
     return p.parse_args(argv)
 
 
@@ -94,7 +97,11 @@ def run_native(args):
     B = args.global_batch
     sweep = [int(b) for b in args.sweep.split(",") if b.strip()]
     cfg = Config(ep_size=world, rank=rank, local_rank=local_rank, per_rank_cap=-(-max([B] + sweep) // world))
-    kw = {"ll_rows": args.ll_rows} if args.native_impl == "dense" else {}
+    kw = {}
+    if args.native_impl == "dense":
+        kw = {"ll_rows": args.ll_rows, "persistent": not args.no_persistent}
+        if args.groups > 0:
+            kw["groups"] = args.groups
     eng = MoEDecodeEngine(cfg, group, impl=args.native_impl, num_layers=NUM_LAYERS, pdl=not args.no_pdl, **kw).build()
     eng.capture()
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
@@ -134,10 +141,12 @@ def run_native(args):
             "impl": f"native-{args.native_impl}",
             "config": {"model": "nemotron-super-shape: 512 experts, top-22, hidden 1024, 88 MoE layers",
                        "global_batch": B, "seq_len": 1, "parallelism": f"ep{world}",
-                       "per_rank_tokens": all_rank_counts(B, world), "transport": eng.dispatcher.heap.transport,
-                       "timing": "one CUDA graph per step; L2 flushed between steps (256 MiB write)",
-                       "pdl": not args.no_pdl, "num_sms": eng.dispatcher.num_sms,
-                       "low_latency_max_global_rows": getattr(eng.dispatcher, "ll_rows", 0)},
+                       "timing": "one CUDA graph per step; L2 flushed between steps (256 MiB write)"},
+            "native_detail": {"per_rank_tokens": all_rank_counts(B, world), "transport": eng.dispatcher.heap.transport,
+                              "pdl": not args.no_pdl, "num_sms": eng.dispatcher.num_sms,
+                              "kernels_per_step": eng.dispatcher.kernel_launches_per_step(NUM_LAYERS),
+                              "pipeline_groups": getattr(eng.dispatcher, "groups", 1),
+                              "low_latency_max_global_rows": getattr(eng.dispatcher, "ll_rows", 0)},
             "e2e": {"value": round(e2e_ms, 4), "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
             "sweep_ms_by_global_batch": {k: round(v, 4) for k, v in sweep_ms.items()},
@@ -264,8 +273,8 @@ def run_reference(args):
             "dtype": "bf16", "data": "synthetic (the reference's own seeded generator)",
             "config": {"model": "nemotron-super-shape: 512 experts, top-22, hidden 1024, 88 MoE layers",
                        "global_batch": B, "seq_len": 1, "parallelism": f"ep{world}",
-                       "timing": "one CUDA graph per step; L2 flushed between steps (256 MiB write)",
-                       "reference_path_reported": best},
+                       "timing": "one CUDA graph per step; L2 flushed between steps (256 MiB write)"},
+            "reference_path_reported": best,
             "reference_ms_by_path": {k: round(v, 4) for k, v in results.items()},
             "e2e": {"value": round(e2e[best], 4), "unit": "ms", "h2d_bytes_per_step": io_bytes[0],
                     "d2h_bytes_per_step": io_bytes[1]},

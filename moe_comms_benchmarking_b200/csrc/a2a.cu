@@ -225,22 +225,14 @@ __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant
   block_barrier_all(c, MCB_SITE_A2A_DISPATCH, 0, ep);
 }
 
-template <bool EMU>
-__global__ void __launch_bounds__(512) a2a_combine_kernel(const __grid_constant__ McbCtx ctx_p,
-                                                          const __grid_constant__ McbA2ACombineArgs args_p,
-                                                          const McbCtx* ectx, const McbA2ACombineArgs* eargs) {
-  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
-  const McbA2ACombineArgs& a = EMU ? eargs[blockIdx.y] : args_p;
+__device__ __forceinline__ void a2a_combine_device(const McbCtx& c, const McbA2ACombineArgs& a, uint32_t launch) {
   __shared__ DestList s_list[kMaxWarps];
-  pdl_wait();
-  pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nwarps = blockDim.x >> 5;
   const int W = c.world;
   int n = *a.n_local;
   if (n < 0) n = 0;
   if (n > a.cap) n = a.cap;
-  const uint32_t launch = next_launch_count(c, MCB_SITE_A2A_COMBINE);
   const bool bmode = n <= (int)gridDim.x;      // one block per token, its warps share the row
   int nwork = bmode ? n : (n + nwarps - 1) / nwarps;
   nwork = nwork < 1 ? 1 : (nwork > (int)gridDim.x ? (int)gridDim.x : nwork);
@@ -331,6 +323,21 @@ __global__ void __launch_bounds__(512) a2a_combine_kernel(const __grid_constant_
     }
     __syncwarp();
   }
+}
+
+template <bool EMU>
+__global__ void __launch_bounds__(512) a2a_combine_kernel(const __grid_constant__ McbCtx ctx_p,
+                                                          const __grid_constant__ McbA2ACombineArgs args_p,
+                                                          const McbCtx* ectx, const McbA2ACombineArgs* eargs) {
+  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
+  const McbA2ACombineArgs& a = EMU ? eargs[blockIdx.y] : args_p;
+  pdl_wait();
+  pdl_launch_dependents();
+  // Block 0 meets the other ranks at launch * world and hands `launch` to the other blocks: the
+  // number must be the same in every block (per-block counters, levelled by the host when the grid
+  // of the site changes).
+  const uint32_t launch = next_launch_count(c, MCB_SITE_A2A_COMBINE);
+  a2a_combine_device(c, a, launch);
 }
 
 }  // namespace mcb

@@ -81,61 +81,13 @@ __global__ void __launch_bounds__(512) agv_kernel(const __grid_constant__ McbCtx
                                                    const McbCtx* ectx, const McbAgvArgs* eargs) {
   const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
   const McbAgvArgs& a = EMU ? eargs[blockIdx.y] : args_p;
-  agv_device(c, a);
+  uint32_t launch = 0;
+  agv_device<-1>(c, a, launch);
 }
 
 // ------------------------------------------------------------------------------------------
 // Reduce-scatter-V
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void acc_bf16x8(float (&acc)[8], uint4 v) {
-  acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x);
-  acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
-  acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z);
-  acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
-}
-
-// Sum of one 16-byte pack over every rank's heap with plain peer loads.
-template <bool F32>
-__device__ __forceinline__ uint4 p2p_reduce_pack(const McbCtx& c, uint64_t off) {
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  int k = 0;
-  for (; k + 4 <= c.world; k += 4) {
-    uint4 v[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      int p = c.rank + k + u;
-      if (p >= c.world) p -= c.world;
-      v[u] = ld_v4_stream(c.heap_peer[p] + off);
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      if (F32) {
-        acc[0] += __uint_as_float(v[u].x); acc[1] += __uint_as_float(v[u].y);
-        acc[2] += __uint_as_float(v[u].z); acc[3] += __uint_as_float(v[u].w);
-      } else {
-        acc_bf16x8(acc, v[u]);
-      }
-    }
-  }
-  for (; k < c.world; ++k) {
-    int p = c.rank + k;
-    if (p >= c.world) p -= c.world;
-    const uint4 v = ld_v4_stream(c.heap_peer[p] + off);
-    if (F32) {
-      acc[0] += __uint_as_float(v.x); acc[1] += __uint_as_float(v.y);
-      acc[2] += __uint_as_float(v.z); acc[3] += __uint_as_float(v.w);
-    } else {
-      acc_bf16x8(acc, v);
-    }
-  }
-  if (F32)
-    return make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]),
-                      __float_as_uint(acc[3]));
-  return make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
-                    pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
-}
-
-
 // Low-latency reduce-scatter-V (bf16): push every valid row of my partial sums to its owner as
 // packets, then sum, for each of my own rows, the packets of all ranks in rank order (fp32).
 __device__ __forceinline__ void rsv_ll(const McbCtx& c, const McbRsvArgs& a, int n, int offset, int valid,
@@ -194,12 +146,7 @@ __device__ __forceinline__ void rsv_ll(const McbCtx& c, const McbRsvArgs& a, int
   }
 }
 
-template <bool EMU>
-__global__ void __launch_bounds__(512) rsv_kernel(const __grid_constant__ McbCtx ctx_p,
-                                                   const __grid_constant__ McbRsvArgs args_p,
-                                                   const McbCtx* ectx, const McbRsvArgs* eargs) {
-  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
-  const McbRsvArgs& a = EMU ? eargs[blockIdx.y] : args_p;
+__device__ __forceinline__ void rsv_device(const McbCtx& c, const McbRsvArgs& a, uint32_t& ll_launch) {
   const int bid = blockIdx.x;
   int n = 0, valid_pre = 0, offset = 0, ep_max = 0, meta_epoch = 0;
   if (a.meta_stable) {
@@ -207,6 +154,7 @@ __global__ void __launch_bounds__(512) rsv_kernel(const __grid_constant__ McbCtx
     valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2]; meta_epoch = a.step_meta[3];
   }
   pdl_wait();
+  ll_launch = next_launch_count(c, MCB_SITE_RSV_LL);
   if (!a.meta_stable) {
     n = *a.n_local;
     valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2]; meta_epoch = a.step_meta[3];
@@ -216,7 +164,7 @@ __global__ void __launch_bounds__(512) rsv_kernel(const __grid_constant__ McbCtx
   const bool bad = n < 0 || n > a.cap || offset < 0 || (long long)offset + n > (long long)a.cap * c.world;
   if (a.ll_rows > 0 && c.world > 1) {
     __shared__ int s_prefix[MCB_MAX_RANKS + 1];
-    const uint32_t flag = ll_next_flag(c, MCB_SITE_RSV_LL);
+    const uint32_t flag = ll_launch;
     if (a.dtype == 0 && valid_pre > 0 && valid_pre <= a.ll_rows) {
       const int valid = valid_pre;
       if (bad || n > a.ll_src_rows) {
@@ -262,34 +210,18 @@ __global__ void __launch_bounds__(512) rsv_kernel(const __grid_constant__ McbCtx
   const long long nvec = (long long)n * a.row_bytes / 16;
   const long long start = (long long)bid * blockDim.x + threadIdx.x;
   const long long stride = (long long)nact * blockDim.x;
-  const uint64_t base = a.src_off + (uint64_t)offset * a.row_bytes;
-  uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
-  if (c.transport == MCB_TRANSPORT_MULTIMEM) {
-    const uint8_t* src = c.heap_mc + base;
-    for (long long i = start; i < nvec; i += stride * kUnroll) {
-      uint4 v[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u)
-        if (i + u * stride < nvec)
-          v[u] = a.dtype == 1 ? mm_ld_reduce_f32x4(src + (i + u * stride) * 16)
-                              : mm_ld_reduce_bf16x8(src + (i + u * stride) * 16);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u)
-        if (i + u * stride < nvec) st_v4(out + (i + u * stride) * 16, v[u]);
-    }
-  } else {
-    for (long long i = start; i < nvec; i += stride * kUnroll) {
-      uint4 v[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u)
-        if (i + u * stride < nvec)
-          v[u] = a.dtype == 1 ? p2p_reduce_pack<true>(c, base + (i + u * stride) * 16)
-                              : p2p_reduce_pack<false>(c, base + (i + u * stride) * 16);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u)
-        if (i + u * stride < nvec) st_v4(out + (i + u * stride) * 16, v[u]);
-    }
-  }
+  reduce_flat(c, reinterpret_cast<uint8_t*>(a.out), a.src_off + (uint64_t)offset * a.row_bytes, nvec, start, stride,
+              a.dtype);
+}
+
+template <bool EMU>
+__global__ void __launch_bounds__(512) rsv_kernel(const __grid_constant__ McbCtx ctx_p,
+                                                   const __grid_constant__ McbRsvArgs args_p,
+                                                   const McbCtx* ectx, const McbRsvArgs* eargs) {
+  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
+  const McbRsvArgs& a = EMU ? eargs[blockIdx.y] : args_p;
+  uint32_t launch = 0;
+  rsv_device(c, a, launch);
 }
 
 // ------------------------------------------------------------------------------------------

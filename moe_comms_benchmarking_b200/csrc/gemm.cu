@@ -381,13 +381,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 dispatch_route_fc1_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ McbGemmArgs a,
                           const __grid_constant__ McbCtx c, const __grid_constant__ McbAgvArgs agv,
                           const __grid_constant__ McbRouteArgs r) {
-  agv_device(c, agv);
-  const uint32_t launch = next_launch_count(c, MCB_SITE_FC1_FUSED);
+  uint32_t ll_launch = 0;
+  agv_device<MCB_SITE_FC1_FUSED>(c, agv, ll_launch);          // waits for the previous kernel first
+  // The arrival counter is back at zero whenever a launch has ended (its last block resets it).
   uint32_t* arrivals = epoch_ptr(c, MCB_SITE_LAYER, 1);
-  grid_sync(c, arrivals, (2u * launch - 1u) * gridDim.x);
+  grid_sync(c, arrivals, gridDim.x);
   route_device(r);
-  grid_sync(c, arrivals, 2u * launch * gridDim.x);
+  grid_sync(c, arrivals, 2u * gridDim.x);
   gemm_device<MCB_GEMM_FC1>(w_map, a);
+  launch_end(c, MCB_SITE_FC1_FUSED, ll_launch, arrivals);
 }
 
 // FC2 GEMM and the cross-rank combine in ONE kernel: the persistent GEMM CTAs finish their
@@ -400,9 +402,11 @@ fc2_combine_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
                    const __grid_constant__ McbCtx c, const __grid_constant__ McbCombineArgs cmb) {
   gemm_device<MCB_GEMM_FC2>(w_map, a);
   // grid-wide barrier: every CTA's y rows are written before any CTA sums them
-  const uint32_t launch = next_launch_count(c, MCB_SITE_FUSED_FC1);
-  grid_sync(c, epoch_ptr(c, MCB_SITE_LAYER, 0), launch * gridDim.x);
+  const uint32_t launch = launch_begin(c, MCB_SITE_FUSED_FC1);
+  uint32_t* arrivals = epoch_ptr(c, MCB_SITE_LAYER, 0);
+  grid_sync(c, arrivals, gridDim.x);
   combine_body(c, cmb);
+  launch_end(c, MCB_SITE_FUSED_FC1, launch, arrivals);
 }
 
 }  // namespace mcb

@@ -91,15 +91,41 @@ __device__ __forceinline__ void block_barrier_all(const McbCtx& c, int site, int
   __syncthreads();
 }
 
-// Per-block launch counter: every block of every launch advances its own counter, whether it
-// has work or not, so the value is the same in all blocks and on all ranks.  Call from all
-// threads of the block; returns the number of this launch (1, 2, ...).
+// Per-block launch counter: every block of every launch advances its own counter, whether it has
+// work or not, so the value is the same in all blocks and on all ranks AS LONG AS every launch on
+// the site uses the same grid; when the grid of a site changes the host levels the whole counter
+// row first (SymmetricHeap.level_launch_counters).  Costs nothing at the end of the kernel, which
+// matters for kernels of a few microseconds.  Call from all threads; returns 1, 2, ...
 __device__ __forceinline__ uint32_t next_launch_count(const McbCtx& c, int site) {
   uint32_t* ctr = epoch_ptr(c, site, blockIdx.x);
   const uint32_t v = *ctr + 1u;
   __syncthreads();
   if (threadIdx.x == 0) *ctr = v;
   return v;
+}
+
+// Launch sequence number of a site (1, 2, ...), the same in every block of a launch and on every
+// rank whatever the grid sizes of this and of earlier launches: word 0 of the site's epoch row counts
+// the launches that have completed and changes only when the LAST block of a launch leaves (word 1
+// counts the blocks that have left).  launch_begin(): all threads, after pdl_wait().  launch_end():
+// all threads of every block, on the way out of the kernel (blocks without work included).  The
+// atomic at the end costs about a microsecond of kernel tail: for long kernels only.
+__device__ __forceinline__ uint32_t launch_begin(const McbCtx& c, int site) {
+  return *reinterpret_cast<volatile uint32_t*>(epoch_ptr(c, site, 0)) + 1u;
+}
+// `also_zero`: a local word (the arrival counter of a grid-wide barrier) that the last block resets too.
+__device__ __forceinline__ void launch_end(const McbCtx& c, int site, uint32_t launch, uint32_t* also_zero = nullptr) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* done = epoch_ptr(c, site, 1);
+    __threadfence();
+    if (atomicAdd(done, 1u) == gridDim.x - 1u) {
+      *reinterpret_cast<volatile uint32_t*>(done) = 0u;
+      if (also_zero) *reinterpret_cast<volatile uint32_t*>(also_zero) = 0u;
+      *reinterpret_cast<volatile uint32_t*>(epoch_ptr(c, site, 0)) = launch;
+      __threadfence();
+    }
+  }
 }
 
 // Bounded spin on a LOCAL word until it reached `target` (wrap-safe).  One thread.

@@ -37,6 +37,10 @@
 #define MCB_SITE_A2A_GO 14       // local hand-over word of the all-to-all combine
 #define MCB_SITE_TEST 15
 #define MCB_SITE_FC1_FUSED 16     // per-block launch counters of the fused dispatch + routing + FC1 kernel
+#define MCB_SITE_STEP_META 17     // count exchange at the start of a persistent decode step (slot 0)
+#define MCB_SITE_STEP 18          // block-matched barrier of each layer of a persistent decode step
+#define MCB_SITE_STEP_CREDIT 19   // per-block count of packet-mode layers (epochs only; the credit words are
+                                  // in a heap region of their own, McbDenseStepArgs::credit_off)
 
 // Status codes written to status[0] (first error wins; 0 = healthy).
 #define MCB_OK 0
@@ -117,6 +121,54 @@ typedef struct {
   int32_t ll_src_rows;         // rows per source region = min(cap, ll_rows)
   int32_t reserved2;
 } McbRsvArgs;
+
+// Words of McbDenseStepArgs::state (local uint32[MCB_STEP_STATE_WORDS], zero at start).  They change
+// only when the last block of a step leaves, so every block of a step reads the same values,
+// whatever the grid size of this or of earlier launches.
+#define MCB_STEP_STATE_WORDS 16
+#define MCB_STATE_STEP_SEQ 0      // steps completed
+#define MCB_STATE_LAYER_BASE 1    // layers completed (its low bit picks the gathered-buffer parity)
+#define MCB_STATE_LL_BASE 2       // packet-mode layers completed (packet flag = this + layer + 1)
+#define MCB_STATE_FINISHED 3      // blocks of the running step that have left
+#define MCB_STATE_GATE0 4         // [MCB_MAX_GROUPS] pushes drained per pipeline group (zero between steps)
+#define MCB_MAX_GROUPS 8
+
+// One whole decode step of the dense dispatcher in ONE persistent kernel: count exchange, then
+// num_layers x (all-gather-V push -> one cross-GPU barrier -> reduce-scatter-V), or, for small
+// steps, num_layers x (packet all-gather, packet reduce-scatter) with no barrier at all.
+typedef struct {
+  const void* src[MCB_MAX_TENSORS];          // local inputs [cap, row]
+  uint64_t dst_off[MCB_MAX_TENSORS];         // heap: [2][cap * world][row] gathered rows, by layer parity
+  uint64_t dst_par_stride[MCB_MAX_TENSORS];  // bytes between the two parities
+  uint32_t row_bytes[MCB_MAX_TENSORS];
+  int32_t num_tensors;
+  int32_t cap;                  // per-rank row capacity
+  int32_t num_layers;
+  int32_t rsv_dtype;            // 0 = bf16 operands with fp32 accumulation, 1 = fp32
+  void* out;                    // local [cap, rsv_row_bytes]
+  uint64_t rsv_off;             // heap: [cap * world][rsv_row_bytes] partial sums of every rank
+  uint32_t rsv_row_bytes;
+  int32_t ll_rows;              // packet mode when the step holds at most this many rows (0 = never)
+  uint64_t agv_ll_off;          // heap: [2][ll_rows][sum(row_bytes) / 8] packets of 16 bytes
+  uint64_t rsv_ll_off;          // heap: [2][world][ll_src_rows][rsv_row_bytes / 8] packets of 16 bytes
+  int32_t ll_src_rows;          // min(cap, ll_rows)
+  int32_t groups;               // pipeline groups of the barrier mode (1 = none)
+  uint64_t group_min_bytes;     // a group must move at least this many bytes per rank and layer
+  const int32_t* n_local;       // device scalar: this rank's row count
+  int32_t* step_meta;           // local int32[8]: valid, offset, max, (kept), step number, parity of the
+                                //   last layer's gathered buffers, mode (0 barrier, 1 packets), groups used
+  uint64_t counts_off;          // heap: int32 counts[2][MCB_MAX_RANKS] of this kernel (by step parity)
+  uint64_t credit_off;          // heap: uint32 credit[grid][MCB_MAX_RANKS] of the packet mode (zero at start)
+  uint32_t* state;              // local uint32[MCB_STEP_STATE_WORDS]
+  // Self-checking build (race tests only): non-zero `check` selects it; the payload is then a hash of
+  // (layer, position) that every receiver verifies, mismatches are counted in *check_errors, and
+  // the rank sleeps delay_ns (at most 1 ms) before every delay_every-th layer.
+  uint32_t* check_errors;
+  int32_t check;
+  int32_t delay_every;
+  uint32_t delay_ns;
+  int32_t reserved0;
+} McbDenseStepArgs;
 
 // All-to-all-V dispatch (one copy of a token per distinct destination rank).
 typedef struct {

@@ -69,6 +69,88 @@ __device__ __forceinline__ void broadcast_flat(const McbCtx& c, const uint8_t* s
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Flat cross-rank reduction: out[i] = sum over ranks of heap[base + 16 * i], 16 bytes at a time.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void acc_bf16x8(float (&acc)[8], uint4 v) {
+  acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x);
+  acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+  acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z);
+  acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+}
+
+// Sum of one 16-byte pack over every rank's heap with plain peer loads.
+template <bool F32>
+__device__ __forceinline__ uint4 p2p_reduce_pack(const McbCtx& c, uint64_t off) {
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  int k = 0;
+  for (; k + 4 <= c.world; k += 4) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int p = c.rank + k + u;
+      if (p >= c.world) p -= c.world;
+      v[u] = ld_v4_stream(c.heap_peer[p] + off);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (F32) {
+        acc[0] += __uint_as_float(v[u].x); acc[1] += __uint_as_float(v[u].y);
+        acc[2] += __uint_as_float(v[u].z); acc[3] += __uint_as_float(v[u].w);
+      } else {
+        acc_bf16x8(acc, v[u]);
+      }
+    }
+  }
+  for (; k < c.world; ++k) {
+    int p = c.rank + k;
+    if (p >= c.world) p -= c.world;
+    const uint4 v = ld_v4_stream(c.heap_peer[p] + off);
+    if (F32) {
+      acc[0] += __uint_as_float(v.x); acc[1] += __uint_as_float(v.y);
+      acc[2] += __uint_as_float(v.z); acc[3] += __uint_as_float(v.w);
+    } else {
+      acc_bf16x8(acc, v);
+    }
+  }
+  if (F32)
+    return make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]),
+                      __float_as_uint(acc[3]));
+  return make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                    pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+}
+
+// dtype 0: bf16 operands summed in fp32 (inside the switch with multimem), 1: fp32.
+__device__ __forceinline__ void reduce_flat(const McbCtx& c, uint8_t* out, uint64_t base, long long nvec,
+                                            long long start, long long stride, int dtype) {
+  if (c.transport == MCB_TRANSPORT_MULTIMEM) {
+    const uint8_t* src = c.heap_mc + base;
+    for (long long i = start; i < nvec; i += stride * kUnroll) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (i + u * stride < nvec)
+          v[u] = dtype == 1 ? mm_ld_reduce_f32x4(src + (i + u * stride) * 16)
+                            : mm_ld_reduce_bf16x8(src + (i + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (i + u * stride < nvec) st_v4(out + (i + u * stride) * 16, v[u]);
+    }
+  } else {
+    for (long long i = start; i < nvec; i += stride * kUnroll) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (i + u * stride < nvec)
+          v[u] = dtype == 1 ? p2p_reduce_pack<true>(c, base + (i + u * stride) * 16)
+                            : p2p_reduce_pack<false>(c, base + (i + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (i + u * stride < nvec) st_v4(out + (i + u * stride) * 16, v[u]);
+    }
+  }
+}
+
 // Number of blocks that take part in a variable collective.  Depends only on values that
 // are identical on every rank (grid size, largest per-rank count, bytes per row), so block b
 // either runs on all ranks or on none.
@@ -110,8 +192,6 @@ __device__ __forceinline__ uint2 ll_wait(const McbCtx& c, const uint8_t* slot, u
     }
   }
 }
-
-__device__ __forceinline__ uint32_t ll_next_flag(const McbCtx& c, int site) { return next_launch_count(c, site); }
 
 __device__ __forceinline__ bool agv_ll_eligible(const McbCtx& c, const McbAgvArgs& a, int valid) {
   if (c.world == 1 || a.ll_rows <= 0 || valid <= 0 || valid > a.ll_rows) return false;
@@ -203,8 +283,12 @@ __device__ __forceinline__ void agv_ll(const McbCtx& c, const McbAgvArgs& a, int
 }
 
 // Body of the variable all-gather, shared by the stand-alone kernel and the fused
-// dispatch + routing + FC1 kernel.  Call from all threads of the block.
-__device__ __forceinline__ void agv_device(const McbCtx& c, const McbAgvArgs& a) {
+// dispatch + routing + FC1 kernel.  Call from all threads of the block.  The launch number (the
+// packet flag) is returned in `ll_launch`: FUSED_SITE < 0 takes it from the per-block counters of
+// MCB_SITE_AGV_LL; otherwise from launch_begin(FUSED_SITE), and the calling kernel must end with
+// launch_end(FUSED_SITE, ll_launch).
+template <int FUSED_SITE>
+__device__ __forceinline__ void agv_device(const McbCtx& c, const McbAgvArgs& a, uint32_t& ll_launch) {
   const int bid = blockIdx.x;
   int n = 0, valid_pre = 0, offset = 0, ep_max = 0;
   if (a.meta_stable) {
@@ -212,6 +296,7 @@ __device__ __forceinline__ void agv_device(const McbCtx& c, const McbAgvArgs& a)
     valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2];
   }
   pdl_wait();
+  ll_launch = FUSED_SITE < 0 ? next_launch_count(c, MCB_SITE_AGV_LL) : launch_begin(c, FUSED_SITE);
   if (!a.meta_stable) {
     n = *a.n_local;
     valid_pre = a.step_meta[0]; offset = a.step_meta[1]; ep_max = a.step_meta[2];
@@ -224,8 +309,7 @@ __device__ __forceinline__ void agv_device(const McbCtx& c, const McbAgvArgs& a)
   pdl_launch_dependents();
   const bool bad = n < 0 || n > a.cap || offset < 0 || (long long)offset + n > (long long)a.cap * c.world;
   if (a.ll_rows > 0 && c.world > 1) {
-    // The launch counter advances on every launch, in either mode.
-    const uint32_t flag = ll_next_flag(c, MCB_SITE_AGV_LL);
+    const uint32_t flag = ll_launch;      // changes with every launch, in either mode
     if (agv_ll_eligible(c, a, valid_pre)) {
       const int valid = valid_pre;
       if (bad) {

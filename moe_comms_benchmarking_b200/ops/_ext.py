@@ -26,7 +26,12 @@ SITE_UNIFORM_AG, SITE_UNIFORM_RS = 5, 6
 SITE_NORM_IN, SITE_NORM_OUT = 7, 8
 SITE_FUSED_FC1, SITE_FUSED_FC2, SITE_LAYER, SITE_TEST = 9, 10, 11, 15
 SITE_AGV_LL, SITE_RSV_LL = 12, 13
-LL_SITES = (SITE_AGV_LL, SITE_RSV_LL)
+SITE_A2A_GO, SITE_FC1_FUSED = 14, 16
+SITE_STEP_META, SITE_STEP, SITE_STEP_CREDIT = 17, 18, 19
+LL_SITES = (SITE_AGV_LL, SITE_RSV_LL, SITE_FC1_FUSED)
+STEP_STATE_WORDS = 16
+STATE_STEP_SEQ, STATE_LAYER_BASE, STATE_LL_BASE, STATE_FINISHED, STATE_GATE0 = 0, 1, 2, 3, 4
+MAX_GROUPS = 8
 
 ERR_NAMES = {0: "ok", 1: "timeout", 2: "capacity", 3: "bounds", 4: "routing", 5: "gemm-timeout"}
 
@@ -63,6 +68,18 @@ class McbRsvArgs(C.Structure):
         ("site", _i32), ("n_local", _vp), ("step_meta", _vp),
         ("ll_off", _u64), ("counts_off", _u64), ("ll_rows", _i32), ("meta_stable", _i32),
         ("ll_src_rows", _i32), ("reserved2", _i32),
+    ]
+
+
+class McbDenseStepArgs(C.Structure):
+    _fields_ = [
+        ("src", _vp * MAX_TENSORS), ("dst_off", _u64 * MAX_TENSORS), ("dst_par_stride", _u64 * MAX_TENSORS),
+        ("row_bytes", _u32 * MAX_TENSORS),
+        ("num_tensors", _i32), ("cap", _i32), ("num_layers", _i32), ("rsv_dtype", _i32),
+        ("out", _vp), ("rsv_off", _u64), ("rsv_row_bytes", _u32), ("ll_rows", _i32),
+        ("agv_ll_off", _u64), ("rsv_ll_off", _u64), ("ll_src_rows", _i32), ("groups", _i32),
+        ("group_min_bytes", _u64), ("n_local", _vp), ("step_meta", _vp), ("counts_off", _u64), ("credit_off", _u64), ("state", _vp),
+        ("check_errors", _vp), ("check", _i32), ("delay_every", _i32), ("delay_ns", _u32), ("reserved0", _i32),
     ]
 
 
@@ -119,7 +136,7 @@ GEMM_FC1, GEMM_FC2 = 0, 1
 _STRUCTS = {
     "ctx": McbCtx, "meta_args": McbMetaArgs, "agv_args": McbAgvArgs, "rsv_args": McbRsvArgs,
     "a2a_dispatch_args": McbA2ADispatchArgs, "a2a_combine_args": McbA2ACombineArgs, "norm_args": McbNormArgs,
-    "gemm_args": McbGemmArgs, "route_args": McbRouteArgs, "combine_args": McbCombineArgs,
+    "dense_step_args": McbDenseStepArgs, "gemm_args": McbGemmArgs, "route_args": McbRouteArgs, "combine_args": McbCombineArgs,
 }
 
 LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libmcb.so"

@@ -106,6 +106,7 @@ class A2ACombinePlan:
 
     def launch(self, pdl: bool = False, stream=None):
         lib = _ext.require()
+        self.heap.level_launch_counters(_ext.SITE_A2A_COMBINE, self.grid)
         _ext.check(lib.mcb_launch_a2a_combine(C.byref(self.heap.ctx()), C.byref(self.args), self.grid,
                                               self.threads, int(pdl), _ext.stream_handle(stream)),
                    "a2a_combine")
@@ -113,6 +114,7 @@ class A2ACombinePlan:
 
 def a2a_decode_step(heap, d: A2ADispatchPlan, c: A2ACombinePlan, num_layers: int, pdl: bool = False, stream=None):
     lib = _ext.require()
+    heap.level_launch_counters(_ext.SITE_A2A_COMBINE, d.grid)
     _ext.check(lib.mcb_a2a_decode_step(C.byref(heap.ctx()), C.byref(d.args), C.byref(c.args), int(num_layers),
                                        d.grid, d.threads, int(pdl), _ext.stream_handle(stream)),
                "a2a_decode_step")

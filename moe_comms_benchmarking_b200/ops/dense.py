@@ -126,6 +126,7 @@ class AllGatherVPlan:
 
     def launch(self, pdl: bool = False, stream=None):
         lib = _ext.require()
+        self.heap.level_launch_counters(_ext.SITE_AGV_LL, self.grid)
         _ext.check(lib.mcb_launch_agv(C.byref(self.heap.ctx()), C.byref(self.args), self.grid, self.threads,
                                       int(pdl), _ext.stream_handle(stream)), "all_gather_v")
 
@@ -167,6 +168,7 @@ class ReduceScatterVPlan:
 
     def launch(self, pdl: bool = False, stream=None):
         lib = _ext.require()
+        self.heap.level_launch_counters(_ext.SITE_RSV_LL, self.grid)
         _ext.check(lib.mcb_launch_rsv(C.byref(self.heap.ctx()), C.byref(self.args), self.grid, self.threads,
                                       int(pdl), _ext.stream_handle(stream)), "reduce_scatter_v")
 
@@ -176,9 +178,109 @@ def dense_decode_step(heap, meta: MetadataPlan, agv: AllGatherVPlan, rsv: Reduce
     """metadata once, then ``num_layers`` x (all-gather-V, reduce-scatter-V), issued by one
     native call (bench_nvls.py:114-121 does this loop in Python)."""
     lib = _ext.require()
+    heap.level_launch_counters(_ext.SITE_AGV_LL, agv.grid)
+    heap.level_launch_counters(_ext.SITE_RSV_LL, agv.grid)
     _ext.check(lib.mcb_dense_decode_step(C.byref(heap.ctx()), C.byref(meta.args), C.byref(agv.args),
                                          C.byref(rsv.args), int(num_layers), agv.grid, agv.threads, int(pdl),
                                          _ext.stream_handle(stream)), "dense_decode_step")
+
+
+def step_credit_bytes(grid: int = _ext.MAX_BLOCKS) -> int:
+    """Heap bytes of the packet-mode credits of the step kernel: one word per (block, source rank)."""
+    return int(grid) * _ext.MAX_RANKS * 4
+
+
+class DenseStepPlan:
+    """One whole decode step as ONE persistent kernel launch (``dense_step_kernel``): the count
+    exchange, then ``num_layers`` x (push -> one cross-GPU barrier -> switch-side reduction), or
+    packets without any barrier when the step holds at most ``ll_rows`` rows.
+
+    ``dsts[i]`` are heap tensors of shape ``[2, cap * world, cols]``: the gathered rows are double
+    buffered by layer parity (the barrier of a layer is then also the fence that protects the readers
+    of the layer before).  After a step, ``step_meta[5]`` names the parity that holds the last layer's
+    rows, ``step_meta[6]`` the mode (0 barrier, 1 packets) and ``step_meta[7]`` the number of
+    pipeline groups used.  ``groups`` > 1 splits the blocks into groups that own a share of every
+    rank's rows and take turns on the push, so that one group's reduction overlaps the next group's
+    push (the two load opposite directions of the links); it needs ``grid`` <= number of SMs."""
+
+    def __init__(self, heap: SymmetricHeap, dsts, srcs, out: torch.Tensor, rsv: HeapTensor, n_local, step_meta,
+                 cap: int, num_layers: int, grid: int = DEFAULT_GRID, threads: int = DEFAULT_THREADS,
+                 agv_ll_stage: HeapTensor | None = None, rsv_ll_stage: HeapTensor | None = None, ll_rows: int = 0,
+                 groups: int = 1, group_min_bytes: int = 256 << 10, state: torch.Tensor | None = None,
+                 credits: HeapTensor | None = None, check_errors: torch.Tensor | None = None, delay_ns: int = 0, delay_every: int = 1):
+        if not (1 <= len(srcs) <= _ext.MAX_TENSORS) or len(srcs) != len(dsts):
+            raise ValueError(f"need 1..{_ext.MAX_TENSORS} (dst, src) pairs")
+        _check_grid(grid, threads)
+        if not (1 <= groups <= _ext.MAX_GROUPS):
+            raise ValueError(f"groups {groups} outside [1, {_ext.MAX_GROUPS}]")
+        if groups > 1 and grid > DEFAULT_GRID:
+            raise ValueError("pipeline groups wait on one another: the grid must not exceed the number of SMs")
+        if step_meta.dtype != torch.int32 or step_meta.numel() < 8:
+            raise ValueError("step_meta must be int32[8]")
+        if n_local.dtype != torch.int32 or n_local.numel() != 1:
+            raise ValueError("n_local must be an int32 scalar tensor on the device")
+        if state is None:
+            state = torch.zeros(_ext.STEP_STATE_WORDS, dtype=torch.int32, device=heap.device)
+        if state.dtype != torch.int32 or state.numel() < _ext.STEP_STATE_WORDS:
+            raise ValueError(f"state must be int32[{_ext.STEP_STATE_WORDS}]")
+        self.heap, self.grid, self.threads, self.state = heap, grid, threads, state
+        self._keep = (list(dsts), list(srcs), out, rsv, n_local, step_meta, agv_ll_stage, rsv_ll_stage)
+        a = _ext.McbDenseStepArgs()
+        gcap = cap * heap.world
+        for i, (d, s) in enumerate(zip(dsts, srcs)):
+            rb = _row_bytes(s)
+            _check_heap_tensor(heap, d, f"dense_step dst[{i}]")
+            if rb % 4:
+                raise ValueError(f"row of tensor {i} is {rb} bytes; must be a multiple of 4")
+            if d.tensor.dtype != s.dtype or d.tensor.dim() != 3 or d.tensor.shape[0] != 2 or d.tensor.shape[2] != s.shape[1]:
+                raise ValueError(f"tensor {i}: gathered buffer must be [2, cap * world, cols] of the source dtype")
+            if s.shape[0] < cap or d.tensor.shape[1] < gcap:
+                raise ValueError(f"tensor {i}: buffers smaller than the capacity")
+            if s.data_ptr() % 16:
+                raise ValueError(f"tensor {i}: source is not 16-byte aligned")
+            a.src[i], a.dst_off[i], a.row_bytes[i] = s.data_ptr(), d.offset, rb
+            a.dst_par_stride[i] = d.tensor.shape[1] * rb
+            if a.dst_par_stride[i] % 16:
+                raise ValueError(f"tensor {i}: parity stride is not 16-byte aligned")
+        rrb = _row_bytes(out)
+        _check_heap_tensor(heap, rsv, "dense_step partial sums")
+        if out.dtype not in (torch.bfloat16, torch.float32) or out.dtype != rsv.tensor.dtype:
+            raise ValueError("combine supports bf16 and fp32, same dtype in and out")
+        if rrb % 16 or out.shape[0] < cap or rsv.nbytes < gcap * rrb:
+            raise ValueError("combine rows must be multiples of 16 bytes and buffers must hold the capacity")
+        a.num_tensors, a.cap, a.num_layers = len(srcs), int(cap), int(num_layers)
+        a.rsv_dtype = 1 if out.dtype == torch.float32 else 0
+        a.out, a.rsv_off, a.rsv_row_bytes = out.data_ptr(), rsv.offset, rrb
+        if ll_rows > 0 and agv_ll_stage is not None and rsv_ll_stage is not None and out.dtype == torch.bfloat16 \
+                and all(_row_bytes(s) % 8 == 0 for s in srcs):
+            need_a = agv_ll_stage_bytes(ll_rows, [_row_bytes(s) for s in srcs])
+            need_r = rsv_ll_stage_bytes(heap.world, ll_rows, cap, rrb)
+            _check_heap_tensor(heap, agv_ll_stage, "dense_step packet staging (gather)")
+            _check_heap_tensor(heap, rsv_ll_stage, "dense_step packet staging (reduce)")
+            if agv_ll_stage.nbytes < need_a or rsv_ll_stage.nbytes < need_r:
+                raise ValueError("packet staging areas are too small")
+            if credits is None or credits.nbytes < step_credit_bytes(grid):
+                raise ValueError(f"packet mode needs a zeroed heap region of {step_credit_bytes(grid)} bytes for its credits")
+            _check_heap_tensor(heap, credits, "dense_step packet credits")
+            a.ll_rows, a.ll_src_rows = int(ll_rows), min(int(cap), int(ll_rows))
+            a.agv_ll_off, a.rsv_ll_off, a.credit_off = agv_ll_stage.offset, rsv_ll_stage.offset, credits.offset
+            self._keep += (credits,)
+        a.groups, a.group_min_bytes = int(groups), int(group_min_bytes)
+        a.n_local, a.step_meta = n_local.data_ptr(), step_meta.data_ptr()
+        a.counts_off, a.state = heap.step_counts_off, state.data_ptr()
+        if check_errors is not None:
+            # self-checking build: hashed payload verified by every receiver, optional per-layer sleep
+            if check_errors.dtype != torch.int32 or check_errors.numel() < 1:
+                raise ValueError("check_errors must be an int32 device counter")
+            a.check_errors, a.check = check_errors.data_ptr(), 1
+            a.delay_ns, a.delay_every = int(delay_ns), max(1, int(delay_every))
+            self._keep += (check_errors,)
+        self.args = a
+
+    def launch(self, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        _ext.check(lib.mcb_launch_dense_step(C.byref(self.heap.ctx()), C.byref(self.args), self.grid, self.threads,
+                                             int(pdl), _ext.stream_handle(stream)), "dense_step")
 
 
 # ---- uniform-count collectives (tensor-parallel style) ------------------------------------------

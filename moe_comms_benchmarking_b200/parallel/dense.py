@@ -8,9 +8,11 @@ per-layer dispatch and combine, ``validate`` with its bit-exact gather check and
 Differences: all inputs live in capacity-sized persistent buffers and the local token count
 is a device scalar, so ONE captured graph serves every batch up to the capacity (the
 reference bakes ``local_tokens`` into the launch and re-captures per batch,
-variable_collectives.py:749,785); the 88-layer loop is issued by one native call; kernels
-can overlap launch latency through programmatic dependent launch; and the transport is
-NVSwitch multicast when available, plain peer access otherwise (EP=1 included).
+variable_collectives.py:749,785); a whole decode step (count exchange + every layer) is ONE
+persistent kernel launch with one cross-GPU barrier per layer (``persistent=True``, the default;
+``persistent=False`` issues the 1 + 2 * layers separate kernels from one native call, with
+programmatic dependent launch between them); and the transport is NVSwitch multicast when
+available, plain peer access otherwise (EP=1 included).
 """
 from __future__ import annotations
 
@@ -19,10 +21,10 @@ import torch.distributed as dist
 
 from ..config import Config
 from ..ops import _ext
-from ..ops.dense import (AllGatherVPlan, MetadataPlan, ReduceScatterVPlan, dense_decode_step, DEFAULT_GRID,
-                         DEFAULT_THREADS, agv_ll_stage_bytes, rsv_ll_stage_bytes)
+from ..ops.dense import (AllGatherVPlan, DenseStepPlan, MetadataPlan, ReduceScatterVPlan, dense_decode_step,
+                         DEFAULT_GRID, DEFAULT_THREADS, agv_ll_stage_bytes, rsv_ll_stage_bytes, step_credit_bytes)
 from .base import Dispatcher
-from .symm_heap import SymmetricHeap, required_bytes
+from .symm_heap import HeapTensor, SymmetricHeap, required_bytes
 
 
 def resolve_ll_rows(cfg: Config, ll_rows: int) -> int:
@@ -40,19 +42,25 @@ class DenseDispatcher(Dispatcher):
 
     def __init__(self, cfg: Config, group, heap: SymmetricHeap | None = None, num_sms: int = DEFAULT_GRID,
                  threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto",
-                 combine_dtype=torch.bfloat16, ll_rows: int = -1, device=None):
+                 combine_dtype=torch.bfloat16, ll_rows: int = -1, persistent: bool = True, groups: int = 1,
+                 group_min_bytes: int = 256 << 10, device=None):
         super().__init__(cfg, group, device)
         self.heap = heap
         self._own_heap = heap is None
-        # A world of one is a local copy: two blocks per SM keep more bytes in flight (measured).
-        self.num_sms = int(num_sms) * (2 if cfg.ep_size == 1 and int(num_sms) == DEFAULT_GRID else 1)
+        self.persistent = bool(persistent)
+        self.num_sms = self._grid_for(cfg, num_sms)
         self.threads = int(threads)
         self.pdl = bool(pdl)
         self.transport = transport
         self.combine_dtype = combine_dtype
         # Low-latency packet mode serves steps that hold at most ll_rows tokens over all ranks.
         self.ll_rows = resolve_ll_rows(cfg, ll_rows)
-        self.kernel_launches_per_step = lambda nl: 1 + 2 * nl
+        self.persistent = bool(persistent)
+        # Pipeline groups of the persistent kernel wait on one another: they need one block per SM.
+        self.groups = int(groups) if cfg.ep_size > 1 else 1
+        self.group_min_bytes = int(group_min_bytes)
+        self.kernel_launches_per_step = lambda nl: 1 if self.persistent else 1 + 2 * nl
+        self._step_plans = {}
 
     @staticmethod
     def _ll_bytes(cfg: Config, ll_rows: int):
@@ -65,8 +73,9 @@ class DenseDispatcher(Dispatcher):
     def heap_specs(cfg: Config, combine_dtype=torch.bfloat16, ll_rows: int = -1):
         g, H, K = max(cfg.global_cap, 1), cfg.hidden, cfg.topk
         a, r = DenseDispatcher._ll_bytes(cfg, ll_rows)
-        return [([g, H], torch.bfloat16), ([g, K], torch.int64), ([g, K], torch.float32), ([g, H], combine_dtype),
-                ([max(a, 16)], torch.uint8), ([max(r, 16)], torch.uint8)]
+        return [([2, g, H], torch.bfloat16), ([2, g, K], torch.int64), ([2, g, K], torch.float32),
+                ([g, H], combine_dtype), ([max(a, 16)], torch.uint8), ([max(r, 16)], torch.uint8),
+                ([step_credit_bytes()], torch.uint8)]
 
     def build(self):
         cfg, dev = self.cfg, self.device
@@ -77,22 +86,29 @@ class DenseDispatcher(Dispatcher):
                                       required_bytes(self.heap_specs(cfg, self.combine_dtype, self.ll_rows)), dev,
                                       transport=self.transport)
         h = self.heap
-        self.agv_h = h.alloc("ep_agv_h", [g, H], torch.bfloat16)
-        self.agv_r = h.alloc("ep_agv_r", [g, K], torch.int64)
-        self.agv_p = h.alloc("ep_agv_p", [g, K], torch.float32)
+        # Gathered rows, double buffered by layer parity for the persistent step kernel; the
+        # stand-alone dispatch and the validation use parity 0.
+        self.agv2_h = h.alloc("ep_agv_h", [2, g, H], torch.bfloat16)
+        self.agv2_r = h.alloc("ep_agv_r", [2, g, K], torch.int64)
+        self.agv2_p = h.alloc("ep_agv_p", [2, g, K], torch.float32)
+        self.agv_h, self.agv_r, self.agv_p = (HeapTensor(t.tensor[0], t.offset, t.nbytes // 2)
+                                              for t in (self.agv2_h, self.agv2_r, self.agv2_p))
         self.rsv = h.alloc("ep_rsv", [g, H], self.combine_dtype)
         a_bytes, r_bytes = self._ll_bytes(cfg, self.ll_rows)
         self.ll_agv = h.alloc("ep_ll_agv", [max(a_bytes, 16)], torch.uint8)
         self.ll_rsv = h.alloc("ep_ll_rsv", [max(r_bytes, 16)], torch.uint8)
+        self.step_credits = h.alloc("ep_step_credit", [step_credit_bytes()], torch.uint8)
         # Persistent local buffers (stable addresses for graph replay).
         self.in_hidden = torch.zeros(cap, H, dtype=torch.bfloat16, device=dev)
         self.in_routing = torch.zeros(cap, K, dtype=torch.int64, device=dev)
         self.in_probs = torch.zeros(cap, K, dtype=torch.float32, device=dev)
         self.out_buf = torch.zeros(cap, H, dtype=self.combine_dtype, device=dev)
         self.n_local = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.step_metadata = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.step_metadata = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.step_state = torch.zeros(_ext.STEP_STATE_WORDS, dtype=torch.int32, device=dev)
         self.local_tokens = 0
         self._make_plans()
+        h.register_reset_hook(self._reset_step_state)
         # Combine timing reduces valid data (bench_nvls.py:81).
         self.rsv.tensor.normal_()
         torch.cuda.synchronize()
@@ -109,10 +125,41 @@ class DenseDispatcher(Dispatcher):
         self.rsv_plan = ReduceScatterVPlan(h, self.out_buf, self.rsv, self.n_local, self.step_metadata, self.cap,
                                            grid=self.num_sms, threads=self.threads,
                                            ll_stage=self.ll_rsv, ll_rows=self.ll_rows)
+        self._step_plans = {}
+
+    def _step_plan(self, num_layers: int) -> DenseStepPlan:
+        plan = self._step_plans.get(num_layers)
+        if plan is None:
+            plan = DenseStepPlan(self.heap, [self.agv2_h, self.agv2_r, self.agv2_p],
+                                 [self.in_hidden, self.in_routing, self.in_probs], self.out_buf, self.rsv,
+                                 self.n_local, self.step_metadata, self.cap, num_layers, grid=self.num_sms,
+                                 threads=self.threads, agv_ll_stage=self.ll_agv, rsv_ll_stage=self.ll_rsv,
+                                 ll_rows=self.ll_rows, credits=self.step_credits,
+                                 groups=self.groups if self.num_sms <= DEFAULT_GRID else 1,
+                                 group_min_bytes=self.group_min_bytes, state=self.step_state)
+            self._step_plans[num_layers] = plan
+        return plan
+
+    def _reset_step_state(self):
+        """After the heap's flags were cleared: restart the sequence words of the step kernel.  The
+        packet flag base keeps growing (staging areas may hold packets with earlier flags) and is
+        made equal on all ranks."""
+        base = self.step_state[_ext.STATE_LL_BASE:_ext.STATE_LL_BASE + 1].to(torch.int64) + 4 * 1024
+        if self.cfg.ep_size > 1:
+            dist.all_reduce(base, op=dist.ReduceOp.MAX, group=self.group)
+        self.step_state.zero_()
+        self.step_state[_ext.STATE_LL_BASE] = int(base.item()) & 0x7FFFFFFF
+        self.step_credits.tensor.zero_()          # the per-block credit counts restart with the epochs
+
+    def _grid_for(self, cfg: Config, num_sms: int) -> int:
+        # A world of one is a local copy: with one kernel per operation two blocks per SM keep more
+        # bytes in flight (measured); the persistent kernel holds one block per SM and unrolls deeper.
+        if self.persistent:
+            return int(num_sms)
+        return int(num_sms) * (2 if cfg.ep_size == 1 and int(num_sms) == DEFAULT_GRID else 1)
 
     def set_num_sms(self, num_sms: int):
-        # A world of one is a local copy: two blocks per SM keep more bytes in flight (measured).
-        self.num_sms = int(num_sms) * (2 if cfg.ep_size == 1 and int(num_sms) == DEFAULT_GRID else 1)
+        self.num_sms = self._grid_for(self.cfg, num_sms)
         if self._built:
             self._make_plans()
 
@@ -144,7 +191,16 @@ class DenseDispatcher(Dispatcher):
         self.rsv_plan.launch(self.pdl)
 
     def decode_step(self, num_layers: int):
-        dense_decode_step(self.heap, self.meta_plan, self.agv_plan, self.rsv_plan, num_layers, self.pdl)
+        if self.persistent:
+            self._step_plan(num_layers).launch(self.pdl)
+        else:
+            dense_decode_step(self.heap, self.meta_plan, self.agv_plan, self.rsv_plan, num_layers, self.pdl)
+
+    def gathered(self):
+        """(hidden, routing, probs) views of the rows gathered by the LAST decode step
+        (host-synchronising: reads the parity word the step kernel wrote)."""
+        par = int(self.step_metadata[5].item()) if self.persistent else 0
+        return self.agv2_h.tensor[par], self.agv2_r.tensor[par], self.agv2_p.tensor[par]
 
     def check_health(self):
         self.heap.check_status()
@@ -189,6 +245,25 @@ class DenseDispatcher(Dispatcher):
             ok = n == 0 or torch.allclose(self.out.float(), w * rsv_full[off:off + n].float(), rtol=2e-2, atol=2e-2)
             results.append((f"dense RSV-V reduce   B={B:<4d}", bool(ok),
                             f"output == world*rsv[global_id] element-wise; local_tokens={n}"))
+            if self.persistent:
+                # the whole step as one persistent kernel: 3 layers, then 2 (both parities end a step)
+                for nl in (3, 2):
+                    for t in (self.agv2_h, self.agv2_r, self.agv2_p):
+                        t.tensor.zero_()
+                    self.out_buf.zero_()
+                    self._sync_all()
+                    self.decode_step(nl)
+                    self._sync_all()
+                    meta = self.step_metadata.tolist()
+                    gh, gr, gp = self.gathered()
+                    ok = (meta[:3] == [valid, off, max(counts)]
+                          and torch.equal(gh[:valid], full_h) and torch.equal(gr[:valid], full_r)
+                          and torch.equal(gp[:valid], full_p)
+                          and (n == 0 or torch.allclose(self.out.float(), w * rsv_full[off:off + n].float(),
+                                                        rtol=2e-2, atol=2e-2)))
+                    results.append((f"dense step kernel    B={B:<4d}", bool(ok),
+                                    f"{nl} layers in one launch: gathered rows bit-exact in parity {meta[5]}, "
+                                    f"output == world*rsv; mode={'packets' if meta[6] else 'barrier'} groups={meta[7]}"))
         try:
             self.check_health()
         except Exception as e:

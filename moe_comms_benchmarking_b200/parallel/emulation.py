@@ -15,7 +15,7 @@ import ctypes as C
 import torch
 
 from ..ops import _ext
-from .symm_heap import ALIGN, FLAGS_BYTES, RESERVED_BYTES, DeviceStatusError, HeapTensor, _align
+from .symm_heap import ALIGN, COUNTS_BYTES, FLAGS_BYTES, RESERVED_BYTES, DeviceStatusError, HeapTensor, _align
 
 
 def _to_device(structs, device) -> torch.Tensor:
@@ -48,6 +48,10 @@ class EmuWorld:
             self.ctxs.append(c)
         self.d_ctx = _to_device(self.ctxs, self.device)
         self.counts_off = FLAGS_BYTES
+        self._site_grid = {}
+        self.step_counts_off = FLAGS_BYTES + COUNTS_BYTES
+        self.step_state = [torch.zeros(_ext.STEP_STATE_WORDS, dtype=torch.int32, device=self.device)
+                           for _ in range(world)]
 
     def alloc(self, shape, dtype) -> list[HeapTensor]:
         n = 1
@@ -59,6 +63,17 @@ class EmuWorld:
             raise MemoryError("emulated heap exhausted")
         self._cursor = _align(off + max(1, n * esize), ALIGN)
         return [HeapTensor(h[off:off + n * esize].view(dtype).view(*shape), off, n * esize) for h in self.heaps]
+
+    def _level(self, site: int, grid: int):
+        """Per-block launch counters need one grid per site: level the row when it changes
+        (what SymmetricHeap.level_launch_counters does for a real rank)."""
+        if self._site_grid.get(site) == grid:
+            return
+        if site in self._site_grid:
+            for e in self.epochs:
+                row = e[site * _ext.MAX_BLOCKS:(site + 1) * _ext.MAX_BLOCKS]
+                row.fill_(int(row.max().item()))
+        self._site_grid[site] = grid
 
     def upload(self, structs) -> torch.Tensor:
         return _to_device(structs, self.device)
@@ -99,6 +114,7 @@ class EmuWorld:
                 a.ll_off, a.ll_rows = ll_stage[r].offset, ll_rows
             args.append(a)
         d = self.upload(args)
+        self._level(_ext.SITE_AGV_LL, grid)
         _ext.check(_ext.require().mcb_emu_agv(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
                                               self.world, grid, threads, self._stream()), "emu agv")
         torch.cuda.synchronize()
@@ -118,8 +134,44 @@ class EmuWorld:
                 a.ll_src_rows = min(cap, ll_rows)
             args.append(a)
         d = self.upload(args)
+        self._level(_ext.SITE_RSV_LL, grid)
         _ext.check(_ext.require().mcb_emu_rsv(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
                                               self.world, grid, threads, self._stream()), "emu rsv")
+        torch.cuda.synchronize()
+
+    def dense_step(self, dsts, srcs, outs, rsv, n_locals, step_metas, cap, num_layers, grid=4, threads=256,
+                   agv_ll_stage=None, rsv_ll_stage=None, ll_rows=0, groups=1, group_min_bytes=0,
+                   check_errors=None, delays_ns=None, delay_every=1):
+        """One persistent decode step on all emulated ranks.  dsts: list over tensors of per-rank
+        HeapTensor lists of shape [2, cap * world, cols]; step_metas: per-rank int32[8]."""
+        args = []
+        for r in range(self.world):
+            a = _ext.McbDenseStepArgs()
+            for i in range(len(srcs)):
+                rb = srcs[i][r].shape[1] * srcs[i][r].element_size()
+                a.src[i], a.dst_off[i], a.row_bytes[i] = srcs[i][r].data_ptr(), dsts[i][r].offset, rb
+                a.dst_par_stride[i] = dsts[i][r].tensor.shape[1] * rb
+            a.num_tensors, a.cap, a.num_layers = len(srcs), cap, num_layers
+            a.rsv_dtype = 1 if outs[r].dtype == torch.float32 else 0
+            a.out, a.rsv_off = outs[r].data_ptr(), rsv[r].offset
+            a.rsv_row_bytes = outs[r].shape[1] * outs[r].element_size()
+            if agv_ll_stage is not None and ll_rows > 0:
+                a.ll_rows, a.ll_src_rows = ll_rows, min(cap, ll_rows)
+                a.agv_ll_off, a.rsv_ll_off = agv_ll_stage[r].offset, rsv_ll_stage[r].offset
+                if getattr(self, "_step_credits", None) is None:
+                    self._step_credits = self.alloc([_ext.MAX_BLOCKS * _ext.MAX_RANKS], torch.int32)
+                a.credit_off = self._step_credits[r].offset
+            a.groups, a.group_min_bytes = groups, group_min_bytes
+            a.n_local, a.step_meta = n_locals[r].data_ptr(), step_metas[r].data_ptr()
+            a.counts_off, a.state = self.step_counts_off, self.step_state[r].data_ptr()
+            if check_errors is not None:
+                a.check_errors, a.check = check_errors[r].data_ptr(), 1
+                a.delay_ns, a.delay_every = (delays_ns[r] if delays_ns else 0), delay_every
+            args.append(a)
+        d = self.upload(args)
+        _ext.check(_ext.require().mcb_emu_dense_step(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
+                                                     C.byref(args[0]), self.world, grid, threads, self._stream()),
+                   "emu dense step")
         torch.cuda.synchronize()
 
     def barrier_test(self, grid=2, rounds=1):
@@ -173,6 +225,7 @@ class EmuWorld:
             a.hidden, a.cap = b["hidden"], b["cap"]
             args.append(a)
         d = self.upload(args)
+        self._level(_ext.SITE_A2A_COMBINE, grid)
         _ext.check(_ext.require().mcb_emu_a2a_combine(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
                                                       self.world, grid, threads, self._stream()), "emu a2a combine")
         torch.cuda.synchronize()

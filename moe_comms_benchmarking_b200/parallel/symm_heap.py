@@ -19,6 +19,7 @@ only ever see raw addresses.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 
 import torch
@@ -28,8 +29,9 @@ from ..ops import _ext
 
 ALIGN = 256
 FLAGS_BYTES = _ext.NUM_SITES * _ext.MAX_BLOCKS * 4
-COUNTS_BYTES = 2 * _ext.MAX_RANKS * 4
-RESERVED_BYTES = ((FLAGS_BYTES + COUNTS_BYTES + ALIGN - 1) // ALIGN) * ALIGN
+COUNTS_BYTES = 2 * _ext.MAX_RANKS * 4          # counts of the metadata kernel (two parities)
+STEP_COUNTS_BYTES = 2 * _ext.MAX_RANKS * 4     # counts of the persistent step kernel (two parities)
+RESERVED_BYTES = ((FLAGS_BYTES + COUNTS_BYTES + STEP_COUNTS_BYTES + ALIGN - 1) // ALIGN) * ALIGN
 
 
 class DeviceStatusError(RuntimeError):
@@ -69,8 +71,14 @@ class HeapTensor:
 class SymmetricHeap:
     """``SymmetricHeap(group, nbytes, device)`` is collective over ``group``."""
 
-    def __init__(self, group, nbytes: int, device, transport: str = "auto", timeout_s: float = 2.0):
+    def __init__(self, group, nbytes: int, device, transport: str = "auto", timeout_s: float = 2.0,
+                 multicast: bool = True):
+        """``multicast=False`` keeps the allocation out of any NVSwitch multicast object (peer
+        mappings only).  Jobs in which a rank may leave while others keep running must use it: a
+        rank that disappears while its memory is bound to a multicast object can raise NVLink
+        faults on the surviving GPUs."""
         self.group = group
+        self.multicast = bool(multicast)
         self.device = torch.device(device)
         self.world = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
@@ -80,6 +88,8 @@ class SymmetricHeap:
         self._handle = None
         self._cursor = RESERVED_BYTES
         self._registry: dict[str, HeapTensor] = {}
+        self._reset_hooks = []
+        self._site_grid: dict[int, int] = {}
         self.peer_ptrs = [0] * self.world
         self.mc_ptr = 0
         on_gpu = self.device.type == "cuda"
@@ -110,13 +120,27 @@ class SymmetricHeap:
                 symm_mem.enable_symm_mem_for_group(self.group.group_name)
             except Exception:
                 pass  # newer versions need no opt-in
-            self.buffer = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
-            self.buffer.zero_()
-            self._handle = symm_mem.rendezvous(self.buffer, self.group.group_name)
+            # PyTorch binds a multicast object during the rendezvous unless this variable is set.
+            prev = os.environ.get("TORCH_SYMM_MEM_DISABLE_MULTICAST")
+            if not self.multicast:
+                os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
+            try:
+                self.buffer = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+                self.buffer.zero_()
+                self._handle = symm_mem.rendezvous(self.buffer, self.group.group_name)
+            finally:
+                if not self.multicast:
+                    if prev is None:
+                        os.environ.pop("TORCH_SYMM_MEM_DISABLE_MULTICAST", None)
+                    else:
+                        os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = prev
             self.peer_ptrs = [int(p) for p in self._handle.buffer_ptrs]
             self.mc_ptr = int(getattr(self._handle, "multicast_ptr", 0) or 0)
+            if not self.multicast and self.mc_ptr:
+                raise RuntimeError("a multicast address was bound although multicast=False was requested")
             if not self.mc_ptr:
-                self.init_failure_reason = "no NVLS multicast object for this group"
+                self.init_failure_reason = ("multicast disabled on request" if not self.multicast
+                                            else "no NVLS multicast object for this group")
             torch.cuda.synchronize()
             dist.barrier(self.group)
         except Exception as e:  # surfaced by callers as a RuntimeError with the reason
@@ -161,6 +185,10 @@ class SymmetricHeap:
     @property
     def counts_off(self) -> int:
         return FLAGS_BYTES
+
+    @property
+    def step_counts_off(self) -> int:
+        return FLAGS_BYTES + COUNTS_BYTES
 
     def peer_view(self, peer: int, ht: HeapTensor) -> torch.Tensor:
         """This rank's mapping of ``peer``'s copy of a heap tensor (debug / validation only)."""
@@ -207,6 +235,24 @@ class SymmetricHeap:
             self.status.zero_()
             raise DeviceStatusError(words)
 
+    def level_launch_counters(self, site: int, grid: int):
+        """Kernels that number their launches with per-block counters (``next_launch_count``) need the
+        same grid on every launch of a site.  Call this (on every rank, at the same point of the
+        program, with nothing in flight on other streams) before the first launch with a new grid:
+        it sets the site's whole counter row to its maximum, so blocks that did not exist under the
+        old grid agree with the others.  A no-op while the grid stays the same."""
+        if self._site_grid.get(site) == grid:
+            return
+        if site in self._site_grid:
+            row = self.epochs[site * _ext.MAX_BLOCKS:(site + 1) * _ext.MAX_BLOCKS]
+            row.fill_(int(row.max().item()))
+        self._site_grid[site] = grid
+
+    def register_reset_hook(self, fn):
+        """``fn()`` runs on every rank inside ``reset_sync_state`` after the flags were cleared (for
+        users of the heap that keep their own sequence words next to the flags)."""
+        self._reset_hooks.append(fn)
+
     def reset_sync_state(self):
         """Collective: zero the flags and epochs on every rank (after an error, or between
         tests).  All kernels must have drained."""
@@ -222,6 +268,8 @@ class SymmetricHeap:
         for s, v in keep.items():
             self.epochs[s * _ext.MAX_BLOCKS:(s + 1) * _ext.MAX_BLOCKS] = v
         self.status.zero_()
+        for fn in self._reset_hooks:
+            fn()
         if self.device.type == "cuda":
             torch.cuda.synchronize()
         if self.world > 1:
@@ -229,6 +277,7 @@ class SymmetricHeap:
 
     def destroy(self):
         self._registry.clear()
+        self._reset_hooks.clear()
         self._handle = None
         self.buffer = None
 

@@ -103,5 +103,5 @@ def test_low_latency_limit_and_heap_sizing():
     assert rsv_ll_stage_bytes(8, 256, 64, 2048) == 2 * 8 * 64 * 256 * 16
     cfg = Config(ep_size=8, per_rank_cap=1024)
     specs = DenseDispatcher.heap_specs(cfg)
-    assert specs[0][0] == [8192, 1024] and len(specs) == 6
-    assert required_bytes(specs) > 8192 * (2048 + 176 + 88 + 2048)
+    assert specs[0][0] == [2, 8192, 1024] and len(specs) == 7     # gathered rows: two layer parities
+    assert required_bytes(specs) > 8192 * (2 * (2048 + 176 + 88) + 2048)

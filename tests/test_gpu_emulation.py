@@ -158,6 +158,50 @@ def test_a2a_dispatch_and_combine_bf16(lib, counts):
     w.check_status()
 
 
+def test_launch_numbers_do_not_depend_on_the_grid(lib):
+    """The launch number that the all-to-all combine hands from block 0 to the other blocks, and the
+    packet flag of the low-latency collectives, are per-block counters that the host levels when the
+    grid of a site changes: a launch with more blocks than any earlier one must neither skip the
+    combine's leading cross-rank barrier nor disagree about the flag.  Every launch uses new data,
+    so a block that ran ahead of the barrier or matched a stale packet produces a wrong result."""
+    W, E, K, H, counts = 4, 32, 6, 256, [5, 2, 8, 3]
+    w, b, xs, idxs, ws, n_locals, cap = _a2a_case(W, E, K, H, counts, False, 19)
+    outs = [torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV) for _ in range(W)]
+    g = torch.Generator(device=DEV).manual_seed(3)
+    for grid in (2, 8, 16, 3, 16):
+        xs = [torch.randn(cap, H, device=DEV, generator=g).to(torch.bfloat16) for _ in range(W)]
+        w.a2a_dispatch(b, xs, idxs, ws, n_locals, E, grid=grid)
+        w.a2a_combine(b, outs, n_locals, grid=grid)
+        for r in range(W):
+            ref = oracle.roundtrip_identity(xs[r][:counts[r]], idxs[r][:counts[r]].cpu(), E, W)
+            assert torch.allclose(outs[r][:counts[r]].float().cpu(), ref, rtol=2e-2, atol=2e-2)
+    w.check_status()
+    # packet mode of the stand-alone all-gather / reduce-scatter with a changing grid
+    from moe_comms_benchmarking_b200.ops.dense import agv_ll_stage_bytes, rsv_ll_stage_bytes
+    cap, LL = 8, 8
+    w = EmuWorld(W, 8 << 20, DEV)
+    dst = w.alloc([cap * W, H], torch.bfloat16)
+    rsv = w.alloc([cap * W, H], torch.bfloat16)
+    st_a = w.alloc([agv_ll_stage_bytes(LL, [H * 2])], torch.uint8)
+    st_r = w.alloc([rsv_ll_stage_bytes(W, LL, cap, H * 2)], torch.uint8)
+    metas, counts = _metas(W), [2, 1, 0, 3]
+    n_locals = _scalars(counts)
+    for grid in (1, 6, 2, 12):
+        src = [torch.randn(cap, H, device=DEV, generator=g).to(torch.bfloat16) for _ in range(W)]
+        w.metadata(n_locals, metas, cap)
+        w.all_gather_v([dst], [src], n_locals, metas, cap, grid, 128, ll_stage=st_a, ll_rows=LL)
+        full = oracle.all_gather_v([src[r][:counts[r]] for r in range(W)])
+        for r in range(W):
+            assert torch.equal(dst[r].tensor[:sum(counts)], full)
+            rsv[r].tensor.copy_(torch.randn(cap * W, H, device=DEV, generator=g).to(torch.bfloat16))
+        outs = [torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV) for _ in range(W)]
+        w.reduce_scatter_v(outs, rsv, n_locals, metas, cap, grid, 128, ll_stage=st_r, ll_rows=LL)
+        want = oracle.reduce_scatter_v([rsv[r].tensor[:sum(counts)].cpu() for r in range(W)], counts)
+        for r in range(W):
+            assert torch.allclose(outs[r][:counts[r]].float().cpu(), want[r], rtol=2e-2, atol=2e-2)
+    w.check_status()
+
+
 def test_a2a_fp8_dispatch(lib):
     W, E, K, H, counts = 2, 16, 4, 512, [6, 3]
     w, b, xs, idxs, ws, n_locals, cap = _a2a_case(W, E, K, H, counts, True, 13)

@@ -39,11 +39,32 @@ def test_dense_dispatcher_validate_and_graph_reuse(world1, pdl):
         g.replay()
         torch.cuda.synchronize()
         assert d.step_metadata[:3].tolist() == [n, 0, n]
-        assert torch.equal(d.agv_h.tensor[:n], h) and torch.equal(d.agv_r.tensor[:n], i)
-        assert torch.equal(d.agv_p.tensor[:n], w)
+        gh, gr, gp = d.gathered()           # the parity the last layer of the step wrote
+        assert torch.equal(gh[:n], h) and torch.equal(gr[:n], i) and torch.equal(gp[:n], w)
         assert torch.equal(d.out, d.rsv.tensor[:n])        # world of one: the sum is the row itself
     d.check_health()
     d.destroy()
+
+
+@pytest.mark.parametrize("persistent", [True, False])
+def test_set_num_sms_on_every_dispatcher(world1, persistent):
+    """Changing the CTA-count knob on a built dispatcher rebuilds its plans and keeps it correct."""
+    from moe_comms_benchmarking_b200.parallel.a2a import A2ADispatcher
+    from moe_comms_benchmarking_b200.parallel.dense import DenseDispatcher
+    from moe_comms_benchmarking_b200.utils.inputs import make_inputs
+    cfg = _cfg(32)
+    for d in (DenseDispatcher(cfg, world1, persistent=persistent), A2ADispatcher(cfg, world1)):
+        d.build()
+        for sms in (16, 148, 64):
+            d.set_num_sms(sms)
+            h, i, w = make_inputs(cfg, 20, "cuda:0")
+            d.setup_batch(h, i, w)
+            d.decode_step(2)
+            torch.cuda.synchronize()
+            d.check_health()
+            for name, ok, detail in d.validate():
+                assert ok, f"{d.name} sms={sms} {name}: {detail}"
+        d.destroy()
 
 
 def test_dense_capacity_overflow_is_reported(world1):
@@ -97,7 +118,7 @@ def test_engine_end_to_end_from_pinned_host(world1):
         out = eng.step_host(h.cpu().pin_memory(), i.cpu().pin_memory(), w.cpu().pin_memory())
         assert out.shape == (n, cfg.hidden)
         assert torch.equal(out, eng.dispatcher.rsv.tensor[:n].cpu())
-        assert torch.equal(eng.dispatcher.agv_h.tensor[:n].cpu(), h.cpu())
+        assert torch.equal(eng.dispatcher.gathered()[0][:n].cpu(), h.cpu())
     eng.check_health()
     eng.destroy()
 
@@ -146,6 +167,6 @@ def test_bench_contract_one_gpu():
     for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
                 "vs_baseline", "dtype", "data", "config", "e2e", "gpu_launches", "clocks"):
         assert key in line, key
-    assert line["n_gpus"] == 1 and line["steps"] == 3 and line["gpu_launches"] == 3 * 177
+    assert line["n_gpus"] == 1 and line["steps"] == 3 and line["gpu_launches"] == 3 * 1      # one persistent kernel per step
     assert line["value"] > 0 and line["e2e"]["value"] >= line["value"] * 0.5
     assert line["e2e"]["h2d_bytes_per_step"] == 8192 * 2312 + 4
