@@ -10,6 +10,7 @@ into ``lib/libmcb.so`` with plain ``nvcc``; there is no JIT and no cache.
 from __future__ import annotations
 
 import argparse
+import fcntl
 import hashlib
 import os
 import shutil
@@ -75,18 +76,31 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and is_current():
         return LIB_PATH
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
-    srcs = sources()
-    if not srcs:
-        raise RuntimeError(f"no .cu sources under {CSRC}")
-    with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
-        results = list(pool.map(lambda s: _compile(s, verbose), srcs))
-    objs = [str(o) for o, _ in results]
-    (LIB_DIR / "ptxas.log").write_text("\n".join(f"=== {s.name} ===\n{log}" for s, (_, log) in zip(srcs, results)))
-    cmd = [_nvcc(), *ARCH_FLAGS, "-shared", "-o", str(LIB_PATH), *objs]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"link failed:\n{res.stdout}{res.stderr}")
-    (LIB_DIR / "build.stamp").write_text(_digest())
+    # Several ranks of one job may get here at once: one builds, the others wait on the lock and
+    # then find the library current.  The library is linked under a temporary name and renamed into
+    # place, so a process that loads it never sees a half-written file.
+    with open(LIB_DIR / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and is_current():
+                return LIB_PATH
+            srcs = sources()
+            if not srcs:
+                raise RuntimeError(f"no .cu sources under {CSRC}")
+            with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
+                results = list(pool.map(lambda s: _compile(s, verbose), srcs))
+            objs = [str(o) for o, _ in results]
+            (LIB_DIR / "ptxas.log").write_text(
+                "\n".join(f"=== {s.name} ===\n{log}" for s, (_, log) in zip(srcs, results)))
+            tmp = LIB_DIR / f".libmcb.{os.getpid()}.so"
+            cmd = [_nvcc(), *ARCH_FLAGS, "-shared", "-o", str(tmp), *objs]
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError(f"link failed:\n{res.stdout}{res.stderr}")
+            os.replace(tmp, LIB_PATH)
+            (LIB_DIR / "build.stamp").write_text(_digest())
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB_PATH
 
 

@@ -160,15 +160,21 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
-        # Build in place when the toolkit is there; otherwise fail loudly (there is no fallback path).
+    from .. import build as _build
+    if not _build.is_current():
+        # Missing, or left over from older sources: build in place when the toolkit is there (one
+        # process at a time: build() takes a file lock and links to a temporary name), otherwise
+        # fail loudly.  There is no fallback path.
         try:
-            from .. import build as _build
             _build.build()
         except Exception as e:
+            if not LIB_PATH.exists():
+                raise ExtensionMissing(
+                    f"{LIB_PATH} is missing and could not be built ({type(e).__name__}: {e}); "
+                    f"run `python -m moe_comms_benchmarking_b200.build`") from e
             raise ExtensionMissing(
-                f"{LIB_PATH} is missing and could not be built ({type(e).__name__}: {e}); "
-                f"run `python -m moe_comms_benchmarking_b200.build`") from e
+                f"{LIB_PATH} was built from other sources than the ones in csrc/ and could not be rebuilt "
+                f"({type(e).__name__}: {e}); run `python -m moe_comms_benchmarking_b200.build`") from e
     lib = C.CDLL(os.fspath(LIB_PATH))
     for name, struct in _STRUCTS.items():
         fn = getattr(lib, f"mcb_sizeof_{name}")

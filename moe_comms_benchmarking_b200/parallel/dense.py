@@ -127,8 +127,8 @@ class DenseDispatcher(Dispatcher):
                                            ll_stage=self.ll_rsv, ll_rows=self.ll_rows)
         self._step_plans = {}
 
-    def _step_plan(self, num_layers: int) -> DenseStepPlan:
-        plan = self._step_plans.get(num_layers)
+    def _step_plan(self, num_layers: int, **check) -> DenseStepPlan:
+        plan = None if check else self._step_plans.get(num_layers)
         if plan is None:
             plan = DenseStepPlan(self.heap, [self.agv2_h, self.agv2_r, self.agv2_p],
                                  [self.in_hidden, self.in_routing, self.in_probs], self.out_buf, self.rsv,
@@ -136,9 +136,39 @@ class DenseDispatcher(Dispatcher):
                                  threads=self.threads, agv_ll_stage=self.ll_agv, rsv_ll_stage=self.ll_rsv,
                                  ll_rows=self.ll_rows, credits=self.step_credits,
                                  groups=self.groups if self.num_sms <= DEFAULT_GRID else 1,
-                                 group_min_bytes=self.group_min_bytes, state=self.step_state)
-            self._step_plans[num_layers] = plan
+                                 group_min_bytes=self.group_min_bytes, state=self.step_state, **check)
+            if not check:
+                self._step_plans[num_layers] = plan
         return plan
+
+    def race_check(self, total_layers: int = 200):
+        """Write-after-read stress of the step kernel on the real transport: steps of 5-8 layers that
+        alternate between packet mode and barrier mode, run with the self-checking payload (a hash of
+        layer number and position that every receiver verifies right after its barrier or poll) while
+        a different rank is slowed down in every step by a bounded sleep per layer.  Returns
+        ``(ok, detail)``; collective."""
+        w, rank = self.cfg.ep_size, self.cfg.rank
+        errs = torch.zeros(1, dtype=torch.int32, device=self.device)
+        small = max(1, min(w + 1, self.ll_rows)) if self.ll_rows > 0 else 0
+        big = min(self.cap * w, max(self.ll_rows + w, 6 * w))
+        done, step, modes = 0, 0, set()
+        saved = int(self.n_local.item())
+        while done < total_layers:
+            B = small if (step % 2 == 0 and small) else big
+            layers = 5 + step % 4
+            self.n_local.fill_(self._validation_counts(B)[rank])
+            delay = 20000 + 3000 * (step % 5) if step % w == rank else (7000 if (step + 2) % w == rank else 0)
+            self._step_plan(layers, check_errors=errs, delay_ns=delay, delay_every=1 + step % 3).launch(self.pdl)
+            modes.add(int(self.step_metadata[6].item()))
+            done += layers
+            step += 1
+        self._sync_all()
+        self.n_local.fill_(saved)
+        bad = int(errs.item())
+        return bad == 0, (f"{done} layers in {step} steps (modes seen: "
+                          f"{'+'.join('packets' if m else 'barrier' for m in sorted(modes))}, groups={self.groups}), "
+                          f"per-rank delays up to 32 us per layer: {bad} payload mismatches")
+
 
     def _reset_step_state(self):
         """After the heap's flags were cleared: restart the sequence words of the step kernel.  The
@@ -264,6 +294,9 @@ class DenseDispatcher(Dispatcher):
                     results.append((f"dense step kernel    B={B:<4d}", bool(ok),
                                     f"{nl} layers in one launch: gathered rows bit-exact in parity {meta[5]}, "
                                     f"output == world*rsv; mode={'packets' if meta[6] else 'barrier'} groups={meta[7]}"))
+        if self.persistent:
+            ok, detail = self.race_check()
+            results.append(("dense step kernel race check", ok, detail))
         try:
             self.check_health()
         except Exception as e:
