@@ -27,10 +27,11 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--only", default="", help="comma-separated subset of route,fc1,fc2,ffn,combine to time")
     args = ap.parse_args(argv)
     from moe_comms_benchmarking_b200.ops import _ext
-    from moe_comms_benchmarking_b200.ops.experts import (ExpertCombinePlan, ExpertWeights, GroupedGemmPlan, RouteBuffers,
-                                                         RoutePlan)
+    from moe_comms_benchmarking_b200.ops.experts import (ExpertCombinePlan, ExpertFfnPlan, ExpertWeights, GroupedGemmPlan,
+                                                         RouteBuffers, RoutePlan)
     from moe_comms_benchmarking_b200.parallel.symm_heap import SymmetricHeap
     dev = "cuda:0"
     torch.cuda.set_device(0)
@@ -44,7 +45,8 @@ def main(argv=None):
     cap = max(tokens)
     heap = SymmetricHeap(None, cap * H * 2 + (1 << 20), dev)
     partial = heap.alloc("partial", [cap, H], torch.bfloat16)
-    weights = ExpertWeights(E, H, I, dev, seed=1)
+    weights = ExpertWeights(E, H, I, dev, seed=1, layout="split")       # tokens-as-rows GEMM kernels
+    weights_il = ExpertWeights(E, H, I, dev, seed=1)                    # weights-as-M FFN kernel (interleaved gate/up)
     route = RouteBuffers(cap, K, E, dev)
     xs = torch.randn(cap, H, device=dev).to(torch.bfloat16)
     idxs = torch.zeros(cap, K, dtype=torch.int64, device=dev)
@@ -59,6 +61,7 @@ def main(argv=None):
         "route": RoutePlan(route, idxs, ws, ntok, expert_begin=0, status=st),
         "fc1": GroupedGemmPlan(_ext.GEMM_FC1, weights.map_gate_up, route, xs, act, 2 * I, H, st),
         "fc2": GroupedGemmPlan(_ext.GEMM_FC2, weights.map_down, route, act, y, H, I, st),
+        "ffn": ExpertFfnPlan(weights_il, route, xs, act, y, st),
         "combine": ExpertCombinePlan(heap, y, route, partial, out, ntok, meta, cap),
     }
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -71,7 +74,11 @@ def main(argv=None):
         ntok.fill_(T)
         meta.copy_(torch.tensor([T, 0, T, 1], dtype=torch.int32))
         times = {}
+        only = [k for k in args.only.split(",") if k]
         for name, plan in plans.items():
+            if only and name not in only:
+                times[name] = float("nan")
+                continue
             for _ in range(args.warmup):
                 for p in plans.values():
                     p.launch()
@@ -101,7 +108,10 @@ def main(argv=None):
               f"fc1 {times['fc1']:7.1f}us ({w1 / times['fc1'] / 1e3:6.0f} GB/s weights, {f1 / times['fc1'] / 1e6:6.0f} useful / "
               f"{f1p / times['fc1'] / 1e6:6.0f} issued TFLOP/s, {100 * frac(times['fc1'], w1 + pairs * (H + I) * 2, f1):4.0f}% of roofline) | "
               f"fc2 {times['fc2']:7.1f}us ({w2 / times['fc2'] / 1e3:6.0f} GB/s, {f2 / times['fc2'] / 1e6:6.0f}/{f2p / times['fc2'] / 1e6:6.0f} TFLOP/s, "
-              f"{100 * frac(times['fc2'], w2 + pairs * (H + I) * 2, f2):4.0f}%) | combine {times['combine']:7.1f}us", flush=True)
+              f"{100 * frac(times['fc2'], w2 + pairs * (H + I) * 2, f2):4.0f}%) | "
+              f"ffn (gate/up + down, weights as M, one launch) {times['ffn']:7.1f}us ({(w1 + w2) / times['ffn'] / 1e3:6.0f} GB/s weights, "
+              f"{100 * frac(times['ffn'], w1 + w2 + pairs * (H + 2 * I + H) * 2, f1 + f2):4.0f}% of roofline) | "
+              f"combine {times['combine']:7.1f}us", flush=True)
 
 
 if __name__ == "__main__":

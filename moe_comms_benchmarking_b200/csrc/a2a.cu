@@ -19,10 +19,10 @@
 //   * optional 1x128 block-scaled e4m3 dispatch: amax over each 128-element block, scale =
 //     amax / 448, saturating convert, fp32 scales shipped next to the rows.
 #include <cstdio>
-#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include "mcb_barrier.cuh"
+#include "mcb_fp8.cuh"
 #include "mcb_launch.h"
 #include "mcb_noalloc.h"
 
@@ -36,27 +36,6 @@ struct DestList {
 };
 
 __device__ __forceinline__ uint32_t warp_or(uint32_t v) { return __reduce_or_sync(0xffffffffu, v); }
-
-// Quantise 8 bf16 values (one 16-byte pack) to 8 e4m3 bytes: saturating RNE of v / scale.
-__device__ __forceinline__ uint2 quant_pack_e4m3(uint4 v, float scale) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-  uint16_t q[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    // true division (not a reciprocal multiply) so results match an fp32 reference bit for bit
-    const float2 f = make_float2(__fdiv_rn(bf16_lo(w[i]), scale), __fdiv_rn(bf16_hi(w[i]), scale));
-    q[i] = (uint16_t)__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
-  }
-  return make_uint2((uint32_t)q[0] | ((uint32_t)q[1] << 16), (uint32_t)q[2] | ((uint32_t)q[3] << 16));
-}
-
-__device__ __forceinline__ float pack_absmax(uint4 v) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-  float m = 0.f;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) m = fmaxf(m, fmaxf(fabsf(bf16_lo(w[i])), fabsf(bf16_hi(w[i]))));
-  return m;
-}
 
 template <bool EMU>
 __global__ void __launch_bounds__(512) a2a_dispatch_kernel(const __grid_constant__ McbCtx ctx_p,

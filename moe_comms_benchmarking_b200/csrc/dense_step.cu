@@ -33,6 +33,12 @@
 // All per-step sizes are read from device memory, so one captured launch serves every batch.
 // Every wait is bounded and reports through the status words.
 //
+// FP8 = true dispatches the hidden rows as 1 x 128 block-scaled e4m3 (BASELINE configuration of the
+// DeepSeek-V3 shape): tensor 0's source is bf16 [cap, hidden], its gathered form is one byte per value,
+// and tensor 3 is the gathered fp32 scales [rows, hidden / 128], produced here; quantisation happens
+// inside the push (barrier mode: 16 neighbouring threads share a block and agree on its largest
+// magnitude with shuffles; packet mode: every thread scans the 256 bytes of its block itself).
+//
 // CHECK = true is the self-checking build used by the race tests: the pushed payload is not the
 // input rows but a hash of (layer sequence number, position), every receiver verifies the words
 // it is entitled to read right after its barrier (or packet poll) and counts mismatches, and a
@@ -43,7 +49,9 @@
 
 #include "mcb_barrier.cuh"
 #include "mcb_dense.cuh"
+#include "mcb_fp8.cuh"
 #include "mcb_launch.h"
+#include "mcb_step.cuh"
 
 namespace mcb {
 
@@ -108,7 +116,19 @@ __device__ __forceinline__ void credit_wait(const McbCtx& c, const McbDenseStepA
 
 // Packet all-gather of one layer.  Slot i = (global row) * wpr + word is sent by thread
 // (i mod nthreads) of the row's owner and read by the same thread index on every rank.
-template <bool CHECK>
+// The 8 payload bytes of word j of gathered tensor t of local row `row` when the hidden rows are
+// quantised on the way out: 8 e4m3 values (t == 0) or two fp32 scales (t == 3).
+__device__ __forceinline__ uint2 fp8_word(const McbDenseStepArgs& a, int row, int t, int j) {
+  const uint8_t* src = reinterpret_cast<const uint8_t*>(a.src[0]) + (uint64_t)row * a.fp8_hidden * 2;
+  if (t == 0) {
+    const float scale = e4m3_scale(block_absmax_serial(src + (uint64_t)(j >> 4) * 256));
+    return quant_pack_e4m3(ld_v4(src + (uint64_t)j * 16), scale);
+  }
+  return make_uint2(__float_as_uint(e4m3_scale(block_absmax_serial(src + (uint64_t)(2 * j) * 256))),
+                    __float_as_uint(e4m3_scale(block_absmax_serial(src + (uint64_t)(2 * j + 1) * 256))));
+}
+
+template <bool CHECK, bool FP8>
 __device__ __forceinline__ void step_agv_ll(const McbCtx& c, const McbDenseStepArgs& a, const StepShape& s,
                                             int n, int offset, int valid, uint32_t flag, uint32_t par,
                                             uint32_t seq, long long gtid, long long nthreads) {
@@ -124,6 +144,8 @@ __device__ __forceinline__ void step_agv_ll(const McbCtx& c, const McbDenseStepA
         const int row = (int)(i / s.wpr);
         int t, j;
         split_word(s, (int)(i - (long long)row * s.wpr), t, j);
+        if (FP8 && (t == 0 || t == 3)) d[u] = fp8_word(a, row - offset, t, j);
+        else
         d[u] = CHECK ? make_uint2(check_word(seq, 0u, (uint32_t)i * 2u), check_word(seq, 0u, (uint32_t)i * 2u + 1u))
                      : ld_v2(reinterpret_cast<const uint8_t*>(a.src[t]) + (uint64_t)(row - offset) * a.row_bytes[t] +
                              (uint64_t)j * 8);
@@ -262,7 +284,46 @@ __device__ __forceinline__ void copy_flat_local(uint8_t* dst, const uint8_t* src
   }
 }
 
-template <bool EMU, bool CHECK>
+// Barrier-mode push of the quantised hidden rows [r0, r1) of this rank and of their scales.  Packs
+// (16 bytes of bf16 = 8 values) are dealt to threads in order, so the 16 lanes of a half warp hold one
+// 128-value block.  Call from all threads of the block (whole warps take part in the shuffles).
+__device__ __forceinline__ void fp8_push(const McbCtx& c, const McbDenseStepArgs& a, uint32_t par, int offset, int r0,
+                                         int r1, long long start, long long stride) {
+  const int H = (int)a.fp8_hidden, ppr = H / 8, nblk = H / 128;
+  const long long total = (long long)(r1 - r0) * ppr;              // a multiple of 16
+  const uint8_t* src = reinterpret_cast<const uint8_t*>(a.src[0]) + (uint64_t)r0 * H * 2;
+  const uint64_t q_off = a.dst_off[0] + (uint64_t)par * a.dst_par_stride[0] + (uint64_t)(offset + r0) * H;
+  const uint64_t s_off = a.dst_off[3] + (uint64_t)par * a.dst_par_stride[3] + (uint64_t)(offset + r0) * nblk * 4;
+  const long long warp_start = start - (threadIdx.x & 31);
+  for (long long base = warp_start; base < total; base += stride) {
+    const long long i = base + (threadIdx.x & 31);
+    const bool live = i < total;
+    const uint4 v = live ? ld_v4_stream(src + i * 16) : make_uint4(0, 0, 0, 0);
+    float amax = pack_absmax(v);
+#pragma unroll
+    for (int sh = 8; sh >= 1; sh >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
+    if (!live) continue;
+    const float scale = e4m3_scale(amax);
+    const uint2 q = quant_pack_e4m3(v, scale);
+    const long long row = i / ppr;
+    const int pk = (int)(i - row * ppr);
+    const uint64_t qo = q_off + (uint64_t)row * H + (uint64_t)pk * 8;
+    const uint64_t so = s_off + ((uint64_t)row * nblk + (pk >> 4)) * 4;
+    if (c.transport == MCB_TRANSPORT_MULTIMEM) {
+      mm_st_v2(c.heap_mc + qo, q);
+      if ((pk & 15) == 0) mm_st_b32(c.heap_mc + so, __float_as_uint(scale));
+    } else {
+      for (int k = 0; k < c.world; ++k) {
+        int p = c.rank + 1 + k;
+        if (p >= c.world) p -= c.world;
+        st_v2(c.heap_peer[p] + qo, q);
+        if ((pk & 15) == 0) st_b32(c.heap_peer[p] + so, __float_as_uint(scale));
+      }
+    }
+  }
+}
+
+template <bool EMU, bool CHECK, bool FP8>
 __global__ void __launch_bounds__(512) dense_step_kernel(const __grid_constant__ McbCtx ctx_p,
                                                          const __grid_constant__ McbDenseStepArgs args_p,
                                                          const McbCtx* ectx, const McbDenseStepArgs* eargs) {
@@ -280,46 +341,8 @@ __global__ void __launch_bounds__(512) dense_step_kernel(const __grid_constant__
                  ll_base = state[MCB_STATE_LL_BASE];
 
   // ---- count exchange -------------------------------------------------------------------------
-  int n = *a.n_local;
-  if (n < 0) n = 0;
-  if (n > a.cap) {
-    if (tid == 0 && bid == 0) report_error(c, MCB_ERR_CAPACITY, MCB_SITE_STEP_META, 0, (uint32_t)n, (uint32_t)a.cap);
-    n = a.cap;
-  }
-  if (W > 1) {
-    const uint32_t par_m = step_seq & 1u;
-    if (bid == 0) {
-      const uint64_t slot_off = a.counts_off + (uint64_t)(par_m * MCB_MAX_RANKS + c.rank) * sizeof(int32_t);
-      if (c.transport == MCB_TRANSPORT_MULTIMEM) {
-        if (tid == 0) mm_st_b32(c.heap_mc + slot_off, (uint32_t)n);
-      } else {
-        for (int p = tid; p < W; p += blockDim.x) st_relaxed_sys(c.heap_peer[p] + slot_off, (uint32_t)n);
-      }
-      __syncthreads();
-      signal_all<true>(c, MCB_SITE_STEP_META, 0);   // the signalling thread is the one that stored
-    }
-    if (tid == 0) wait_flag(c, MCB_SITE_STEP_META, 0, (step_seq + 1u) * (uint32_t)W);
-    __syncthreads();
-    const uint8_t* counts = c.heap_local + a.counts_off + (uint64_t)par_m * MCB_MAX_RANKS * sizeof(int32_t);
-    for (int p = tid; p < W; p += blockDim.x) s_cnt[p] = (int)ld_relaxed_sys(counts + p * 4);
-  } else if (tid == 0) {
-    s_cnt[0] = n;
-  }
-  __syncthreads();
-  if (tid == 0) {
-    int run = 0, mx = 0;
-    for (int p = 0; p < W; ++p) {
-      int v = s_cnt[p];
-      if (v < 0) v = 0;
-      if (v > a.cap) v = a.cap;
-      s_prefix[p] = run;
-      run += v;
-      mx = v > mx ? v : mx;
-    }
-    s_prefix[W] = run;
-    s_max = mx;
-  }
-  __syncthreads();
+  const int n = step_count_exchange(c, MCB_SITE_STEP_META, a.counts_off, step_seq, *a.n_local, a.cap, s_cnt, s_prefix,
+                                    &s_max);
   const int valid = s_prefix[W], offset = s_prefix[c.rank], ep_max = s_max;
 
   StepShape shp;
@@ -374,7 +397,7 @@ __global__ void __launch_bounds__(512) dense_step_kernel(const __grid_constant__
         if (l >= 2) credit_wait(c, a, cb + (uint32_t)l - 1u);
         if (CHECK && a.delay_ns && (l + c.rank) % (a.delay_every < 1 ? 1 : a.delay_every) == 0)
           __nanosleep(a.delay_ns > 1000000u ? 1000000u : a.delay_ns);
-        step_agv_ll<CHECK>(c, a, shp, n, offset, valid, flag, par, layer_base + (uint32_t)l, gtid, nthreads);
+        step_agv_ll<CHECK, FP8>(c, a, shp, n, offset, valid, flag, par, layer_base + (uint32_t)l, gtid, nthreads);
         __syncthreads();      // the block holds all its gathered words before it starts the combine
         step_rsv_ll(c, a, s_prefix, n, ep_max, flag, gtid, nthreads);
         __syncthreads();
@@ -402,9 +425,11 @@ __global__ void __launch_bounds__(512) dense_step_kernel(const __grid_constant__
         if (tid == 0 && need) wait_local(c, a.state + MCB_STATE_GATE0 + prev, need, MCB_SITE_STEP);
         __syncthreads();
       }
+      if (FP8) fp8_push(c, a, par, offset, r0, r1, start, stride);
 #pragma unroll
       for (int t = 0; t < MCB_MAX_TENSORS; ++t) {
         if (t >= a.num_tensors) break;
+        if (FP8 && (t == 0 || t == 3)) continue;      // quantised values and scales: pushed above
         const uint32_t rb = a.row_bytes[t];
         const uint8_t* src = reinterpret_cast<const uint8_t*>(a.src[t]) + (uint64_t)r0 * rb;
         const uint64_t dst_off = a.dst_off[t] + (uint64_t)par * a.dst_par_stride[t] + (uint64_t)(offset + r0) * rb;
@@ -485,7 +510,13 @@ static int check_step_args(const McbDenseStepArgs* a, int grid, int threads) {
   if ((a->rsv_row_bytes & 15u) || !a->state || !a->step_meta || !a->n_local || !a->out) return 1;
   if (a->ll_rows > 0 && (a->credit_off == 0 || (a->credit_off & 3u))) return 1;
   for (int t = 0; t < a->num_tensors; ++t)
-    if ((a->row_bytes[t] & 3u) || !a->src[t]) return 1;
+    if ((a->row_bytes[t] & 3u) || (!a->src[t] && !(a->fp8_hidden && t == 3))) return 1;
+  if (a->fp8_hidden) {
+    // quantised dispatch: tensor 0 = one byte per value, tensor 3 = one fp32 scale per 128 values
+    if (a->check || a->num_tensors != 4 || a->fp8_hidden % 128u || a->row_bytes[0] != a->fp8_hidden ||
+        a->row_bytes[3] != a->fp8_hidden / 128u * 4u)
+      return 1;
+  }
   return 0;
 }
 
@@ -496,10 +527,13 @@ int mcb_launch_dense_step(const McbCtx* ctx, const McbDenseStepArgs* args, int g
   if (!ctx || check_step_args(args, grid, threads)) return cudaErrorInvalidValue;
   const bool coop = args->groups > 1;
   if (args->check)
-    return launch_kernel(dense_step_kernel<false, true>, dim3(grid), dim3(threads), 0, stream, pdl, coop, *ctx, *args,
-                         (const McbCtx*)nullptr, (const McbDenseStepArgs*)nullptr);
-  return launch_kernel(dense_step_kernel<false, false>, dim3(grid), dim3(threads), 0, stream, pdl, coop, *ctx, *args,
-                       (const McbCtx*)nullptr, (const McbDenseStepArgs*)nullptr);
+    return launch_kernel(dense_step_kernel<false, true, false>, dim3(grid), dim3(threads), 0, stream, pdl, coop, *ctx,
+                         *args, (const McbCtx*)nullptr, (const McbDenseStepArgs*)nullptr);
+  if (args->fp8_hidden)
+    return launch_kernel(dense_step_kernel<false, false, true>, dim3(grid), dim3(threads), 0, stream, pdl, coop, *ctx,
+                         *args, (const McbCtx*)nullptr, (const McbDenseStepArgs*)nullptr);
+  return launch_kernel(dense_step_kernel<false, false, false>, dim3(grid), dim3(threads), 0, stream, pdl, coop, *ctx,
+                       *args, (const McbCtx*)nullptr, (const McbDenseStepArgs*)nullptr);
 }
 
 int mcb_emu_dense_step(const McbCtx* d_ctx, const McbDenseStepArgs* d_args, const McbDenseStepArgs* h_args0,
@@ -508,10 +542,13 @@ int mcb_emu_dense_step(const McbCtx* d_ctx, const McbDenseStepArgs* d_args, cons
   McbCtx dummy{};
   McbDenseStepArgs dargs{};
   if (h_args0->check)
-    return launch_kernel(dense_step_kernel<true, true>, dim3(grid, world), dim3(threads), 0, stream, 0, true, dummy,
-                         dargs, d_ctx, d_args);
-  return launch_kernel(dense_step_kernel<true, false>, dim3(grid, world), dim3(threads), 0, stream, 0, true, dummy,
-                       dargs, d_ctx, d_args);
+    return launch_kernel(dense_step_kernel<true, true, false>, dim3(grid, world), dim3(threads), 0, stream, 0, true,
+                         dummy, dargs, d_ctx, d_args);
+  if (h_args0->fp8_hidden)
+    return launch_kernel(dense_step_kernel<true, false, true>, dim3(grid, world), dim3(threads), 0, stream, 0, true,
+                         dummy, dargs, d_ctx, d_args);
+  return launch_kernel(dense_step_kernel<true, false, false>, dim3(grid, world), dim3(threads), 0, stream, 0, true,
+                       dummy, dargs, d_ctx, d_args);
 }
 
 }  // extern "C"

@@ -30,6 +30,7 @@
 #include "mcb_gemm.h"
 #include "mcb_launch.h"
 #include "mcb_route.cuh"
+#include "mcb_tc.cuh"
 
 namespace mcb {
 
@@ -45,130 +46,9 @@ constexpr int kTmemCols = 512;
 constexpr int kNumThreads = 320;                 // 10 warps
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 
-// ---- mbarrier / TMA / tcgen05 wrappers -------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-
-struct Abort {
-  volatile int* flag;        // shared: set once any wait of this CTA ran out
-  uint32_t* status;          // global status words (may be null)
-  uint64_t timeout_ns;
-};
-
-__device__ __forceinline__ uint64_t now_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Bounded wait.  Returns false once this CTA has given up (now or earlier).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const Abort& ab, uint32_t where) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = now_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 32; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*ab.flag) return false;
-    if (now_ns() - t0 > ab.timeout_ns) {
-      *ab.flag = 1;
-      if (ab.status && atomicCAS(ab.status, 0u, (uint32_t)MCB_GEMM_ERR_TIMEOUT) == 0u) {
-        ab.status[1] = where;
-        ab.status[2] = blockIdx.x;
-        ab.status[3] = parity;
-      }
-      return false;
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      :: "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-
-// Asynchronous 16-byte global -> shared copy (L2 only), and "arrive on this mbarrier once all
-// my earlier cp.async copies have landed" (counts as one of the barrier's expected arrivals).
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(smem_dst)), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
-}
-// D[tmem] (+)= A[smem] * B[smem], bf16 inputs, fp32 accumulate, M=128 N=256 K=16.
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      :: "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// 32 lanes x 16 consecutive fp32 columns -> 16 registers per thread (thread = lane = row).
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
-// 8-row groups 1024 bytes apart (tile base 1024-byte aligned).
-__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address
-  d |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024u >> 4) << 32;                    // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                               // descriptor version (sm_100)
-  d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
-  return d;
-}
-
 // Instruction descriptor: D=f32, A=B=bf16, both K-major, N=256, M=128.
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockN >> 3) << 17) |
                                 ((uint32_t)(kBlockM >> 4) << 24);
-
-__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 template <int MODE>
 __device__ __forceinline__ void gemm_device(const CUtensorMap& w_map, const McbGemmArgs& a) {
@@ -357,19 +237,6 @@ template <int MODE>
 __global__ void __launch_bounds__(kNumThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ McbGemmArgs a) {
   gemm_device<MODE>(w_map, a);
-}
-
-// Grid-wide barrier of a cooperative launch: `arrivals` only ever grows; the caller passes
-// the total it must reach (a multiple of the grid size derived from its launch counter).
-__device__ __forceinline__ void grid_sync(const McbCtx& c, uint32_t* arrivals, uint32_t target) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(arrivals, 1u);
-    wait_local(c, arrivals, target, MCB_SITE_LAYER);
-    __threadfence();
-  }
-  __syncthreads();
 }
 
 // Dispatch, routing and FC1 in ONE kernel: every CTA first pushes its share of this rank's

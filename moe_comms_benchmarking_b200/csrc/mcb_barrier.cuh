@@ -145,4 +145,17 @@ __device__ __forceinline__ bool wait_local(const McbCtx& c, const uint32_t* word
   }
 }
 
+// Grid-wide barrier of a cooperative launch: `arrivals` only ever grows; the caller passes
+// the total it must reach (a multiple of the grid size derived from its launch counter).
+__device__ __forceinline__ void grid_sync(const McbCtx& c, uint32_t* arrivals, uint32_t target) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(arrivals, 1u);
+    wait_local(c, arrivals, target, MCB_SITE_LAYER);
+    __threadfence();
+  }
+  __syncthreads();
+}
+
 }  // namespace mcb

@@ -39,6 +39,8 @@
 #define MCB_SITE_FC1_FUSED 16     // per-block launch counters of the fused dispatch + routing + FC1 kernel
 #define MCB_SITE_STEP_META 17     // count exchange at the start of a persistent decode step (slot 0)
 #define MCB_SITE_STEP 18          // block-matched barrier of each layer of a persistent decode step
+#define MCB_SITE_A2A_STEP_META 20 // count exchange at the start of a persistent all-to-all step (slot 0)
+#define MCB_SITE_A2A_STEP 21      // block-matched barrier of each layer of a persistent all-to-all step
 #define MCB_SITE_STEP_CREDIT 19   // per-block count of packet-mode layers (epochs only; the credit words are
                                   // in a heap region of their own, McbDenseStepArgs::credit_off)
 
@@ -167,7 +169,9 @@ typedef struct {
   int32_t check;
   int32_t delay_every;
   uint32_t delay_ns;
-  int32_t reserved0;
+  // Non-zero: tensor 0's source is bf16 [cap, fp8_hidden] and is dispatched as 1 x 128 block-scaled e4m3
+  // (row_bytes[0] = fp8_hidden bytes), with the fp32 scales as gathered tensor 3 (src[3] unused).
+  uint32_t fp8_hidden;
 } McbDenseStepArgs;
 
 // All-to-all-V dispatch (one copy of a token per distinct destination rank).
@@ -191,6 +195,39 @@ typedef struct {
   int32_t fp8;
   int32_t reserved0;
 } McbA2ADispatchArgs;
+
+// One whole decode step of the all-to-all dispatcher in ONE persistent kernel: count exchange, then
+// num_layers x (push every token's row and routing to each distinct destination rank -> one
+// block-matched cross-GPU barrier -> pull the expert outputs back and sum them).  A token keeps its
+// own index as its slot on every destination (receive layout [parity][source][cap]), so no slot
+// counters exist; a row is valid on the destination when the stamp in its metadata row equals the
+// layer's sequence number (McbA2AStepArgs::step_meta[4] after the step).
+typedef struct {
+  const void* x;               // [cap, hidden] bf16
+  const int64_t* topk_idx;     // [cap, topk]
+  const float* topk_w;         // [cap, topk] (may be NULL: weights of 1)
+  void* out;                   // [cap, hidden] bf16
+  const int32_t* n_local;
+  uint64_t recv_x_off;         // heap: [2][world][cap][hidden] bf16, or e4m3 bytes when fp8 != 0
+  uint64_t recv_scale_off;     // heap: [2][world][cap][hidden/128] fp32 (fp8 only)
+  uint64_t recv_meta_off;      // heap: [2][world][cap][meta_row_bytes]: {stamp, source token, (expert id i32, weight f32) x topk}
+  uint64_t y_off;              // heap: [2][world][cap][hidden] bf16 expert outputs (== recv_x_off for the identity expert in bf16)
+  uint64_t x_par_stride;       // bytes between the two parities of each buffer
+  uint64_t scale_par_stride;
+  uint64_t meta_par_stride;
+  uint64_t y_par_stride;
+  uint32_t meta_row_bytes;     // 8 + 8 * topk rounded up to 16
+  int32_t hidden;
+  int32_t topk;
+  int32_t num_experts;
+  int32_t cap;
+  int32_t fp8;
+  int32_t num_layers;
+  int32_t reserved0;
+  int32_t* step_meta;          // local int32[8]: valid, offset, max, -, step number, parity of the last layer, -, stamp of the last layer
+  uint64_t counts_off;         // heap: int32 counts[2][MCB_MAX_RANKS] of this kernel
+  uint32_t* state;             // local uint32[MCB_STEP_STATE_WORDS] (step_seq, layer_base, -, finished)
+} McbA2AStepArgs;
 
 // All-to-all-V combine: out[t,:] = sum over destination ranks d of y_d[rank][slot_map[t][d],:].
 typedef struct {

@@ -1,0 +1,302 @@
+// Grouped SwiGLU expert FFN for decode-size batches on the 5th-generation tensor cores, with the
+// operands swapped: the WEIGHTS are the M = 128 operand and the tokens of one expert are the small N.
+//
+// The reference has no expert computation at all (identity expert, bench_nvls.py:109-112).  At
+// decode sizes an expert sees a handful of tokens (3 at a global batch of 64, 170 at 4096 with 512
+// experts / top-22), and a layer is bound by streaming 6 MB of weights per expert.  With tokens as
+// the M operand every expert costs a full 128-row MMA and experts with more than 128 tokens read
+// their weights once per 128 tokens; here
+//   * a work unit is 128 weight rows x the whole reduction length (256 KB of bf16 at K = 1024) of
+//     one expert, multiplied with ALL tokens of that expert in one pass: D[128, N] += W[128, K] X[N, K]^T
+//     with N = the expert's token count rounded up to 16 (up to 256 per pass, accumulators double
+//     buffered in TMEM), so an MMA costs N / 256 of the padded one and every weight byte is read once;
+//   * both projections run in ONE persistent kernel: units 0 .. E * 2I/128 are the gate/up blocks,
+//     the rest the down blocks, dealt round-robin over the CTAs, so the weight stream does not stop
+//     at a kernel boundary.  A down block of expert e waits until all gate/up blocks of e have
+//     stored their activations (a counter per expert; every CTA meets all its gate/up blocks before
+//     its first down block, so the wait cannot deadlock);
+//   * the gate/up matrix is stored interleaved (row 2i = gate row i, row 2i + 1 = up row i), so a
+//     128-row block yields 64 finished activations: the two values meet in neighbouring TMEM lanes
+//     and are exchanged with one shuffle;
+//   * weights arrive by TMA (128 rows x 64 columns per stage, 128-byte swizzle, no multicast), token
+//     rows by asynchronous 16-byte copies through the pair -> token list (the routing permute fused
+//     into the operand load) into the same swizzled K-major layout; the number of pipeline stages
+//     grows as the token tile shrinks (11 stages of 18 KB at N = 16, 4 of 48 KB at N = 256);
+//   * one elected thread issues tcgen05.mma; every mbarrier wait is bounded and reports through the
+//     status words.
+#pragma once
+#include "mcb_tc.cuh"
+
+namespace mcb {
+
+constexpr int kFfnThreads = 320;            // 10 warps: TMA, MMA, 4 epilogue, 4 token-row producers
+constexpr int kFfnRowsM = 128;              // weight rows per unit
+constexpr int kFfnBlockK = 64;              // 128 bytes of bf16
+constexpr int kFfnMaxN = 256;               // tokens per pass
+constexpr int kFfnMaxStages = 12;
+constexpr int kFfnABytes = kFfnRowsM * kFfnBlockK * 2;           // 16 KiB
+constexpr int kFfnPipeBytes = 196 * 1024;
+constexpr int kFfnSmemBytes = kFfnPipeBytes + 1024 /*align*/ + 512 /*barriers*/;
+
+__device__ __forceinline__ int ld_acquire_gpu_i32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_bf16(void* p, float v) {
+  *reinterpret_cast<__nv_bfloat16*>(p) = __float2bfloat16_rn(v);
+}
+
+struct FfnUnit {
+  int fc;          // 0 = gate/up block, 1 = down block
+  int e;           // local expert
+  int j;           // 128-row block inside the expert's matrix
+  int row0;        // first pair row of the expert
+  int rows;        // pair rows of the expert
+};
+
+__device__ __forceinline__ FfnUnit ffn_unit(const McbFfnArgs& a, int u, int n1, int n2) {
+  FfnUnit r;
+  const int u1 = a.num_local_experts * n1;
+  r.fc = u >= u1;
+  const int v = r.fc ? u - u1 : u;
+  const int per = r.fc ? n2 : n1;
+  r.e = v / per;
+  r.j = v - r.e * per;
+  r.row0 = a.expert_offset[r.e];
+  r.rows = a.expert_offset[r.e + 1] - r.row0;
+  return r;
+}
+
+// Call from all kFfnThreads threads of every CTA of the grid; dynamic shared memory of at least
+// kFfnSmemBytes.  `w1_map` covers the interleaved gate/up matrix [E * 2I, H], `w2_map` the down
+// matrix [E * H, I] (both row-major bf16, boxes of 128 rows x 64 columns).
+__device__ __forceinline__ void ffn_device(const CUtensorMap* w1_map, const CUtensorMap* w2_map, const McbFfnArgs& a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kFfnPipeBytes);
+  uint64_t* full = bars;                             // [kFfnMaxStages]
+  uint64_t* empty = bars + kFfnMaxStages;            // [kFfnMaxStages]
+  uint64_t* tfull = bars + 2 * kFfnMaxStages;        // [2]
+  uint64_t* tempty = bars + 2 * kFfnMaxStages + 2;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kFfnMaxStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kFfnMaxStages; ++s) { mbar_init(&full[s], 1 + 128); mbar_init(&empty[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const Abort ab{abort_flag, a.status, a.timeout_ns};
+
+  const int H = a.hidden, I = a.intermediate;
+  const int n1 = 2 * I / kFfnRowsM, n2 = H / kFfnRowsM;
+  const int total_units = a.num_local_experts * (n1 + n2);
+  // Token tile of this launch: the largest expert, rounded up to 16, at most kFfnMaxN per pass.
+  int max_rows = *a.max_rows;
+  if (max_rows < 1) max_rows = 1;
+  const int n_slot = max_rows >= kFfnMaxN ? kFfnMaxN : ((max_rows + 15) & ~15);
+  const int stage_bytes = kFfnABytes + n_slot * 128;
+  int stages = kFfnPipeBytes / stage_bytes;
+  if (stages > kFfnMaxStages) stages = kFfnMaxStages;
+
+  if (warp == 0) {
+    // ---------------- TMA producer: 128 weight rows x 64 columns per stage ----------------
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        const FfnUnit un = ffn_unit(a, u, n1, n2);
+        if (un.rows <= 0) continue;
+        const CUtensorMap* map = un.fc ? w2_map : w1_map;
+        const int k_blocks = (un.fc ? I : H) / kFfnBlockK;
+        const int wrow = un.e * (un.fc ? H : 2 * I) + un.j * kFfnRowsM;
+        for (int c0 = 0; c0 < un.rows && ok; c0 += kFfnMaxN) {
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!(ok = mbar_wait(&empty[s], ph ^ 1u, ab, 11))) break;
+            mbar_arrive_expect_tx(&full[s], kFfnABytes);
+            tma_load_2d(smem + s * stage_bytes, map, &full[s], kb * kFfnBlockK, wrow);
+            if (++s == stages) { s = 0; ph ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      int acc = 0; uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        const FfnUnit un = ffn_unit(a, u, n1, n2);
+        if (un.rows <= 0) continue;
+        const int k_blocks = (un.fc ? I : H) / kFfnBlockK;
+        for (int c0 = 0; c0 < un.rows && ok; c0 += kFfnMaxN) {
+          const int n = un.rows - c0 < kFfnMaxN ? un.rows - c0 : kFfnMaxN;
+          const uint32_t idesc = umma_idesc_bf16(kFfnRowsM, (uint32_t)((n + 15) & ~15));
+          if (!(ok = mbar_wait(&tempty[acc], acc_ph ^ 1u, ab, 12))) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kFfnMaxN);
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!(ok = mbar_wait(&full[s], ph, ab, 13))) break;
+            fence_proxy_async_smem();           // the token rows were written by cp.async, not by TMA
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * stage_bytes);
+            const uint64_t da = make_sw128_desc(sa), db = make_sw128_desc(sa + kFfnABytes);
+#pragma unroll
+            for (int kk = 0; kk < kFfnBlockK / 16; ++kk)
+              umma_bf16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb | kk) != 0);
+            umma_commit(&empty[s]);
+            if (++s == stages) { s = 0; ph ^= 1u; }
+          }
+          if (!ok) break;
+          umma_commit(&tfull[acc]);
+          if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------- epilogue: TMEM (lane = weight row, column = token) -> global ----------------
+    const int q = warp & 3;                  // TMEM lane quarter this warp may read
+    int acc = 0; uint32_t acc_ph = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const FfnUnit un = ffn_unit(a, u, n1, n2);
+      if (un.rows <= 0) continue;
+      for (int c0 = 0; c0 < un.rows && ok; c0 += kFfnMaxN) {
+        const int n = un.rows - c0 < kFfnMaxN ? un.rows - c0 : kFfnMaxN;
+        if (!(ok = mbar_wait(&tfull[acc], acc_ph, ab, 14))) break;
+        tc_fence_after();
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kFfnMaxN);
+        const long long prow0 = (long long)un.row0 + c0;
+        if (!un.fc) {
+          // rows alternate gate / up: lane pairs (2i, 2i + 1) hold the two halves of activation i
+          const int feat = un.j * (kFfnRowsM / 2) + q * 16 + (lane >> 1);
+          const bool odd = lane & 1;
+          uint8_t* obase = reinterpret_cast<uint8_t*>(a.act) + (long long)feat * 2;
+#pragma unroll 1
+          for (int cc = 0; cc < n; cc += 16) {
+            uint32_t v[16];
+            tmem_ld16(t_row + cc, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              // the even lane finishes columns cc .. cc+7, the odd lane columns cc+8 .. cc+15
+              const uint32_t send = odd ? v[i] : v[8 + i];
+              const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
+              const float g = __uint_as_float(odd ? recv : v[i]);
+              const float up = __uint_as_float(odd ? v[8 + i] : recv);
+              const int col = cc + (odd ? 8 : 0) + i;
+              if (col < n) st_bf16(obase + (prow0 + col) * (long long)I * 2, silu(g) * up);
+            }
+          }
+        } else {
+          const int feat = un.j * kFfnRowsM + q * 32 + lane;
+          uint8_t* obase = reinterpret_cast<uint8_t*>(a.y) + (long long)feat * 2;
+#pragma unroll 1
+          for (int cc = 0; cc < n; cc += 16) {
+            uint32_t v[16];
+            tmem_ld16(t_row + cc, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int col = cc + i;
+              if (col < n) {
+                const float p = a.pair_prob ? a.pair_prob[prow0 + col] : 1.0f;
+                st_bf16(obase + (prow0 + col) * (long long)H * 2, __uint_as_float(v[i]) * p);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+        if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+      }
+      if (!un.fc && ok) {
+        // This warp's quarter of the gate/up block is stored: count it for the expert's down blocks
+        // (four counts per block; no barrier between the warps, so nothing can wait for a warp that
+        // has given up).
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(&a.ffn_done[un.e], 1);
+      }
+    }
+  } else {
+    // ---------------- token-row producers: gather rows into the swizzled K-major B tile ----------------
+    const int t = threadIdx.x - 6 * 32;      // 0..127: rows t and t + 128 of the token tile
+    int s = 0; uint32_t ph = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      const FfnUnit un = ffn_unit(a, u, n1, n2);
+      if (un.rows <= 0) continue;
+      const int k_blocks = (un.fc ? I : H) / kFfnBlockK;
+      if (un.fc) {
+        // the activations of this expert are complete once all its gate/up blocks have been counted
+        // (four epilogue warps each); one lane per producer warp polls, bounded
+        if (lane == 0) {
+          const uint64_t t0 = now_ns();
+          while (ld_acquire_gpu_i32(&a.ffn_done[un.e]) < 4 * n1) {
+            if (*ab.flag) break;
+            if (now_ns() - t0 > ab.timeout_ns) {
+              *ab.flag = 1;
+              if (ab.status && atomicCAS(ab.status, 0u, (uint32_t)MCB_GEMM_ERR_TIMEOUT) == 0u) {
+                ab.status[1] = 15; ab.status[2] = blockIdx.x; ab.status[3] = (uint32_t)un.e;
+              }
+              break;
+            }
+          }
+        }
+        __syncwarp();
+      }
+      const uint64_t src_row_bytes = un.fc ? (uint64_t)I * 2 : a.x_row_bytes;
+      for (int c0 = 0; c0 < un.rows && ok; c0 += kFfnMaxN) {
+        const int n = un.rows - c0 < kFfnMaxN ? un.rows - c0 : kFfnMaxN;
+        const uint8_t* src[2];
+        bool live[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = t + h * 128;
+          live[h] = r < n;
+          long long srow = 0;
+          if (live[h]) srow = un.fc ? (long long)un.row0 + c0 + r : (long long)a.pair_token[un.row0 + c0 + r];
+          src[h] = reinterpret_cast<const uint8_t*>(un.fc ? a.act : a.x) + srow * src_row_bytes;
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(&empty[s], ph ^ 1u, ab, 16))) break;
+          uint8_t* sb = smem + s * stage_bytes + kFfnABytes;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (live[h]) {
+              const int r = t + h * 128;
+              uint8_t* dst = sb + r * 128;
+              const uint8_t* g = src[h] + (long long)kb * (kFfnBlockK * 2);
+#pragma unroll
+              for (int c = 0; c < 8; ++c) cp_async_16(dst + ((c ^ (r & 7)) << 4), g + c * 16);
+            }
+          }
+          cp_async_arrive_noinc(&full[s]);     // arrives when this thread's copies have landed
+          if (++s == stages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) __nanosleep(50000);        // let any copy still in flight land before the CTA goes away
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace mcb

@@ -3,6 +3,8 @@
 #pragma once
 #include <stdint.h>
 
+#include "mcb_ctx.h"
+
 #define MCB_GEMM_FC1 0          // gate/up projection + SwiGLU epilogue
 #define MCB_GEMM_FC2 1          // down projection + per-row scale epilogue
 #define MCB_GEMM_ERR_TIMEOUT 5  // status code: a bounded mbarrier wait ran out
@@ -29,6 +31,26 @@ typedef struct {
   uint64_t timeout_ns;
 } McbGemmArgs;
 
+// Grouped SwiGLU FFN with the weights as the M operand (mcb_ffn.cuh): both projections in one
+// persistent kernel over the pair lists written by the routing.
+typedef struct {
+  const void* x;               // gathered tokens [T, hidden] bf16
+  uint64_t x_row_bytes;
+  const int32_t* pair_token;   // [P] pair row -> gathered token
+  const float* pair_prob;      // [P] routing weight of each pair row (NULL: 1)
+  const int32_t* expert_offset;  // [E_loc + 1] first pair row of each local expert
+  const int32_t* max_rows;     // device scalar: largest pair count of one expert
+  void* act;                   // [P, intermediate] bf16 (written by the gate/up blocks, read by the down blocks)
+  void* y;                     // [P, hidden] bf16 = prob * (act . Wd^T)
+  int32_t* ffn_done;           // [E_loc] quarter-blocks of gate/up finished (zeroed by the routing)
+  int32_t num_local_experts;
+  int32_t hidden;              // multiple of 128
+  int32_t intermediate;        // multiple of 64
+  int32_t reserved0;
+  uint32_t* status;
+  uint64_t timeout_ns;
+} McbFfnArgs;
+
 // Routing of the gathered tokens to this rank's experts.
 typedef struct {
   const int64_t* topk_idx;     // gathered [T, topk]
@@ -53,6 +75,8 @@ typedef struct {
   int32_t max_tiles;           // capacity of the tile table
   uint32_t* status;
   uint64_t timeout_ns;
+  int32_t* max_rows;           // device scalar: largest number of pair rows of one expert (may be NULL)
+  int32_t* ffn_done;           // [E_loc] gate/up blocks finished per expert, set to zero here (may be NULL)
 } McbRouteArgs;
 
 // Local pre-sum of each token's expert outputs + cross-rank reduce-scatter.
@@ -71,4 +95,19 @@ typedef struct {
 
 #ifdef __cplusplus
 }
+#endif
+
+#ifdef MCB_WITH_LAYER_ARGS
+// Everything one MoE layer needs, as ONE kernel parameter (or one element of a device array when
+// several ranks are emulated inside one launch): the two weight tensor maps first (64-byte aligned),
+// then the context and the argument blocks of the four phases.
+typedef struct alignas(64) {
+  CUtensorMap w1;              // interleaved gate/up matrix [E * 2I, H]
+  CUtensorMap w2;              // down matrix [E * H, I]
+  McbCtx ctx;
+  McbAgvArgs agv;
+  McbRouteArgs route;
+  McbFfnArgs ffn;
+  McbCombineArgs cmb;
+} McbLayerArgs;
 #endif

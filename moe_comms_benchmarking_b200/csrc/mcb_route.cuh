@@ -21,6 +21,60 @@ __device__ __forceinline__ bool spin_until_ge(const volatile int* p, int target,
   }
 }
 
+// Exclusive prefix of the per-expert pair counts s_cnt[0..E) into a.expert_offset[0..E], the
+// 128-row tile table of the tokens-as-rows GEMMs, the largest count, and the per-expert "gate/up
+// blocks done" counters of the fused FFN back at zero.  One warp: every lane owns a contiguous
+// run of experts, the runs are joined with a shuffle scan (E <= 1024 means at most 32 experts per
+// lane, instead of a serial walk over all of them on one thread).  Call from the 32 threads of
+// ONE warp; s_cnt must be visible to them.  Returns the total in every lane.
+__device__ __forceinline__ int route_offsets(const McbRouteArgs& a, const int* s_cnt, int* s_off, int E) {
+  const int lane = threadIdx.x & 31;
+  const int per = (E + 31) / 32;
+  const int e0 = lane * per, e1 = e0 + per < E ? e0 + per : E;
+  int rows = 0, tiles = 0, mx = 0;
+  for (int e = e0; e < e1; ++e) {
+    const int c = s_cnt[e];
+    rows += c;
+    tiles += (c + 127) >> 7;
+    mx = c > mx ? c : mx;
+  }
+  int row_pre = rows, tile_pre = tiles;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int r = __shfl_up_sync(0xffffffffu, row_pre, o), t = __shfl_up_sync(0xffffffffu, tile_pre, o);
+    if (lane >= o) { row_pre += r; tile_pre += t; }
+  }
+  const int total = __shfl_sync(0xffffffffu, row_pre, 31), total_tiles = __shfl_sync(0xffffffffu, tile_pre, 31);
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  int run = row_pre - rows, tile = tile_pre - tiles;
+  for (int e = e0; e < e1; ++e) {
+    const int c = s_cnt[e];
+    if (s_off) s_off[e] = run;
+    a.expert_offset[e] = run;
+    if (a.ffn_done) a.ffn_done[e] = 0;
+    for (int r0 = 0; r0 < c; r0 += 128, ++tile) {
+      if (tile < a.max_tiles) {
+        a.tile_expert[tile] = e;
+        a.tile_row0[tile] = run + r0;
+        a.tile_rows[tile] = c - r0 < 128 ? c - r0 : 128;
+      }
+    }
+    run += c;
+  }
+  if (lane == 0) {
+    a.expert_offset[E] = total;
+    if (a.max_rows) *a.max_rows = mx;
+    if (total_tiles > a.max_tiles || total > a.max_pairs) {
+      if (a.status && atomicCAS(a.status, 0u, (uint32_t)MCB_ERR_CAPACITY) == 0u) {
+        a.status[1] = 100; a.status[2] = (uint32_t)total_tiles; a.status[3] = (uint32_t)total;
+      }
+    }
+    *a.num_m_tiles = total_tiles < a.max_tiles ? total_tiles : a.max_tiles;
+  }
+  return total;
+}
+
 // One launch, two phases separated by a "last block computes the offsets" hand-over; blocks of
 // the same launch wait for it on a local counter, so the grid must be co-resident (<= #SMs).
 // Call from all threads of every block of the grid.
@@ -53,25 +107,9 @@ __device__ __forceinline__ void route_device(const McbRouteArgs& a) {
         if (e[u] >= 0 && e[u] < E) atomicAdd(&s_hist[(int)e[u]], 1);
     }
     __syncthreads();
-    if (tid == 0) {
-      int run = 0, tiles = 0;
-      for (int e = 0; e < E; ++e) {
-        const int c = s_hist[e];
-        s_hist[e] = run;
-        a.expert_offset[e] = run;
-        for (int r0 = 0; r0 < c; r0 += 128) {
-          if (tiles < a.max_tiles) {
-            a.tile_expert[tiles] = e;
-            a.tile_row0[tiles] = run + r0;
-            a.tile_rows[tiles] = c - r0 < 128 ? c - r0 : 128;
-          }
-          ++tiles;
-        }
-        run += c;
-      }
-      a.expert_offset[E] = run;
-      *a.num_m_tiles = tiles < a.max_tiles ? tiles : a.max_tiles;
-    }
+    if (tid < 32) route_offsets(a, s_hist, s_cursor, E);     // offsets land in s_cursor ...
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) { s_hist[e] = s_cursor[e]; s_cursor[e] = 0; }   // ... and move over
     __syncthreads();
     for (int i0 = tid; i0 < (int)entries; i0 += blockDim.x * 4) {
       long long e[4];
@@ -134,32 +172,15 @@ __device__ __forceinline__ void route_device(const McbRouteArgs& a) {
     // Last block: exclusive prefix over experts, row-tile table, then release the others.
     for (int e = tid; e < E; e += blockDim.x) s_hist[e] = *reinterpret_cast<volatile int*>(&a.expert_count[e]);
     __syncthreads();
-    if (tid == 0) {
-      int run = 0, tiles = 0;
-      for (int e = 0; e < E; ++e) {
-        const int c = s_hist[e];
-        a.expert_offset[e] = run;
-        for (int r0 = 0; r0 < c; r0 += 128) {
-          if (tiles < a.max_tiles) {
-            a.tile_expert[tiles] = e;
-            a.tile_row0[tiles] = run + r0;
-            a.tile_rows[tiles] = c - r0 < 128 ? c - r0 : 128;
-          }
-          ++tiles;
-        }
-        run += c;
+    if (tid < 32) {
+      route_offsets(a, s_hist, nullptr, E);
+      __threadfence();                   // every lane's table entries before the hand-over below
+      __syncwarp();
+      if (tid == 0) {
+        a.sync[0] = 0;
+        __threadfence();
+        atomicAdd(&a.sync[2], 1);
       }
-      a.expert_offset[E] = run;
-      if (tiles > a.max_tiles || run > a.max_pairs) {
-        if (a.status && atomicCAS(a.status, 0u, (uint32_t)MCB_ERR_CAPACITY) == 0u) {
-          a.status[1] = 100; a.status[2] = (uint32_t)tiles; a.status[3] = (uint32_t)run;
-        }
-        tiles = tiles > a.max_tiles ? a.max_tiles : tiles;
-      }
-      *a.num_m_tiles = tiles;
-      a.sync[0] = 0;
-      __threadfence();
-      atomicAdd(&a.sync[2], 1);
     }
   }
   if (tid == 0) {

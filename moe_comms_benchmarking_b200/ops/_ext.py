@@ -28,6 +28,7 @@ SITE_FUSED_FC1, SITE_FUSED_FC2, SITE_LAYER, SITE_TEST = 9, 10, 11, 15
 SITE_AGV_LL, SITE_RSV_LL = 12, 13
 SITE_A2A_GO, SITE_FC1_FUSED = 14, 16
 SITE_STEP_META, SITE_STEP, SITE_STEP_CREDIT = 17, 18, 19
+SITE_A2A_STEP_META, SITE_A2A_STEP = 20, 21
 LL_SITES = (SITE_AGV_LL, SITE_RSV_LL, SITE_FC1_FUSED)
 STEP_STATE_WORDS = 16
 STATE_STEP_SEQ, STATE_LAYER_BASE, STATE_LL_BASE, STATE_FINISHED, STATE_GATE0 = 0, 1, 2, 3, 4
@@ -79,7 +80,7 @@ class McbDenseStepArgs(C.Structure):
         ("out", _vp), ("rsv_off", _u64), ("rsv_row_bytes", _u32), ("ll_rows", _i32),
         ("agv_ll_off", _u64), ("rsv_ll_off", _u64), ("ll_src_rows", _i32), ("groups", _i32),
         ("group_min_bytes", _u64), ("n_local", _vp), ("step_meta", _vp), ("counts_off", _u64), ("credit_off", _u64), ("state", _vp),
-        ("check_errors", _vp), ("check", _i32), ("delay_every", _i32), ("delay_ns", _u32), ("reserved0", _i32),
+        ("check_errors", _vp), ("check", _i32), ("delay_every", _i32), ("delay_ns", _u32), ("fp8_hidden", _u32),
     ]
 
 
@@ -91,6 +92,17 @@ class McbA2ADispatchArgs(C.Structure):
         ("slot_map", _vp), ("send_count", _vp), ("n_local", _vp),
         ("hidden", _i32), ("topk", _i32), ("num_experts", _i32), ("cap", _i32), ("fp8", _i32),
         ("reserved0", _i32),
+    ]
+
+
+class McbA2AStepArgs(C.Structure):
+    _fields_ = [
+        ("x", _vp), ("topk_idx", _vp), ("topk_w", _vp), ("out", _vp), ("n_local", _vp),
+        ("recv_x_off", _u64), ("recv_scale_off", _u64), ("recv_meta_off", _u64), ("y_off", _u64),
+        ("x_par_stride", _u64), ("scale_par_stride", _u64), ("meta_par_stride", _u64), ("y_par_stride", _u64),
+        ("meta_row_bytes", _u32), ("hidden", _i32), ("topk", _i32), ("num_experts", _i32), ("cap", _i32),
+        ("fp8", _i32), ("num_layers", _i32), ("reserved0", _i32),
+        ("step_meta", _vp), ("counts_off", _u64), ("state", _vp),
     ]
 
 
@@ -121,6 +133,16 @@ class McbRouteArgs(C.Structure):
         ("pair_token", _vp), ("pair_prob", _vp), ("pair_pos", _vp),
         ("tile_expert", _vp), ("tile_row0", _vp), ("tile_rows", _vp), ("num_m_tiles", _vp), ("sync", _vp),
         ("max_pairs", _i32), ("max_tiles", _i32), ("status", _vp), ("timeout_ns", _u64),
+        ("max_rows", _vp), ("ffn_done", _vp),
+    ]
+
+
+class McbFfnArgs(C.Structure):
+    _fields_ = [
+        ("x", _vp), ("x_row_bytes", _u64), ("pair_token", _vp), ("pair_prob", _vp), ("expert_offset", _vp),
+        ("max_rows", _vp), ("act", _vp), ("y", _vp), ("ffn_done", _vp),
+        ("num_local_experts", _i32), ("hidden", _i32), ("intermediate", _i32), ("reserved0", _i32),
+        ("status", _vp), ("timeout_ns", _u64),
     ]
 
 
@@ -131,12 +153,27 @@ class McbCombineArgs(C.Structure):
     ]
 
 
+class McbLayerArgs(C.Structure):
+    """One MoE layer as one kernel parameter: two 128-byte tensor maps, then the context and the
+    argument blocks of the four phases (64-byte aligned as a whole)."""
+    _pack_ = 0
+    _fields_ = [
+        ("w1", C.c_uint8 * 128), ("w2", C.c_uint8 * 128), ("ctx", McbCtx), ("agv", McbAgvArgs),
+        ("route", McbRouteArgs), ("ffn", McbFfnArgs), ("cmb", McbCombineArgs),
+    ]
+
+
+def layer_args_size() -> int:
+    """sizeof(McbLayerArgs) as the C compiler sees it (rounded up to its 64-byte alignment)."""
+    return (C.sizeof(McbLayerArgs) + 63) // 64 * 64
+
+
 GEMM_FC1, GEMM_FC2 = 0, 1
 
 _STRUCTS = {
     "ctx": McbCtx, "meta_args": McbMetaArgs, "agv_args": McbAgvArgs, "rsv_args": McbRsvArgs,
-    "a2a_dispatch_args": McbA2ADispatchArgs, "a2a_combine_args": McbA2ACombineArgs, "norm_args": McbNormArgs,
-    "dense_step_args": McbDenseStepArgs, "gemm_args": McbGemmArgs, "route_args": McbRouteArgs, "combine_args": McbCombineArgs,
+    "a2a_dispatch_args": McbA2ADispatchArgs, "a2a_combine_args": McbA2ACombineArgs, "a2a_step_args": McbA2AStepArgs, "norm_args": McbNormArgs,
+    "dense_step_args": McbDenseStepArgs, "gemm_args": McbGemmArgs, "ffn_args": McbFfnArgs, "route_args": McbRouteArgs, "combine_args": McbCombineArgs,
 }
 
 LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libmcb.so"
@@ -182,6 +219,10 @@ def load():
         got, want = fn(), C.sizeof(struct)
         if got != want:
             raise ExtensionMissing(f"layout drift: sizeof({name}) is {got} in libmcb.so, {want} in ctypes")
+    lib.mcb_sizeof_layer_args.restype = C.c_int
+    if lib.mcb_sizeof_layer_args() != layer_args_size():
+        raise ExtensionMissing(f"layout drift: sizeof(layer_args) is {lib.mcb_sizeof_layer_args()} in libmcb.so, "
+                               f"{layer_args_size()} in ctypes")
     lib.mcb_error_string.restype = C.c_char_p
     lib.mcb_error_string.argtypes = [C.c_int]
     _lib = lib

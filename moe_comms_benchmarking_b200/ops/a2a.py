@@ -112,6 +112,97 @@ class A2ACombinePlan:
                    "a2a_combine")
 
 
+def a2a_meta_row_bytes(topk: int) -> int:
+    """Bytes of a packed metadata row of the step kernel: {stamp, token, (expert id, weight) x topk}, in 16-byte chunks."""
+    return (8 + 8 * topk + 15) // 16 * 16
+
+
+class A2AStepBuffers:
+    """Heap buffers of the persistent all-to-all step kernel, double buffered by layer parity:
+    ``recv_x [2, world, cap, hidden]`` (bf16, or e4m3 bytes with ``recv_scale [2, world, cap, hidden/128]``),
+    ``recv_meta [2, world, cap, meta_row_bytes]`` and the expert outputs ``y`` (the received rows themselves
+    for the identity expert in bf16).  A token's slot on every destination is its own index."""
+
+    def __init__(self, heap: SymmetricHeap, cap: int, hidden: int, topk: int, fp8: bool, prefix: str = "a2as"):
+        w = heap.world
+        self.cap, self.hidden, self.topk, self.fp8 = cap, hidden, topk, fp8
+        self.meta_row_bytes = a2a_meta_row_bytes(topk)
+        if hidden % 8 or (fp8 and hidden % 128):
+            raise ValueError("hidden must be a multiple of 8 (128 with fp8 dispatch)")
+        if fp8:
+            self.recv_x = heap.alloc(f"{prefix}_recv_x8", [2, w, cap, hidden], torch.uint8)
+            self.recv_scale = heap.alloc(f"{prefix}_recv_scale", [2, w, cap, hidden // 128], torch.float32)
+            self.y = heap.alloc(f"{prefix}_y", [2, w, cap, hidden], torch.bfloat16)
+        else:
+            self.recv_x = heap.alloc(f"{prefix}_recv_x", [2, w, cap, hidden], torch.bfloat16)
+            self.recv_scale = None
+            self.y = self.recv_x
+        self.recv_meta = heap.alloc(f"{prefix}_recv_meta", [2, w, cap, self.meta_row_bytes], torch.uint8)
+
+    @staticmethod
+    def specs(world: int, cap: int, hidden: int, topk: int, fp8: bool):
+        s = [([2, world, cap, a2a_meta_row_bytes(topk)], torch.uint8)]
+        if fp8:
+            s += [([2, world, cap, hidden], torch.uint8), ([2, world, cap, hidden // 128], torch.float32),
+                  ([2, world, cap, hidden], torch.bfloat16)]
+        else:
+            s += [([2, world, cap, hidden], torch.bfloat16)]
+        return s
+
+    def meta_fields(self, par: int, src: int, rows: int):
+        """(stamp int32 [rows], token int32 [rows], expert ids int32 [rows, topk], weights fp32 [rows, topk]) of the
+        metadata rows received from ``src`` in parity ``par``."""
+        raw = self.recv_meta.tensor[par, src, :rows]
+        words = raw.view(torch.int32).view(rows, -1)
+        ids = words[:, 2:2 + 2 * self.topk:2]
+        wts = words[:, 3:3 + 2 * self.topk:2].view(torch.float32) if rows else words[:, 3:3].view(torch.float32)
+        return words[:, 0], words[:, 1], ids, wts
+
+
+class A2AStepPlan:
+    """One whole decode step of the all-to-all dispatcher as ONE persistent launch (``a2a_step_kernel``)."""
+
+    def __init__(self, heap: SymmetricHeap, bufs: A2AStepBuffers, x, topk_idx, topk_w, out, n_local, step_meta,
+                 num_experts: int, num_layers: int, grid: int = DEFAULT_GRID, threads: int = DEFAULT_THREADS,
+                 state: torch.Tensor | None = None):
+        _check_grid(grid, threads)
+        if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != bufs.hidden or not x.is_contiguous():
+            raise ValueError("x must be contiguous bf16 [rows, hidden]")
+        if topk_idx.dtype != torch.int64 or topk_idx.shape[1] != bufs.topk or not topk_idx.is_contiguous():
+            raise ValueError("topk_idx must be contiguous int64 [rows, topk]")
+        if topk_w is not None and (topk_w.dtype != torch.float32 or not topk_w.is_contiguous()):
+            raise ValueError("topk_w must be contiguous fp32 [rows, topk]")
+        if out.dtype != torch.bfloat16 or out.shape[1] != bufs.hidden or min(x.shape[0], topk_idx.shape[0], out.shape[0]) < bufs.cap:
+            raise ValueError("input and output buffers must hold `cap` rows of `hidden` bf16 values")
+        if num_experts % heap.world:
+            raise ValueError("num_experts must be divisible by the world size")
+        if step_meta.dtype != torch.int32 or step_meta.numel() < 8:
+            raise ValueError("step_meta must be int32[8]")
+        for name in ("recv_x", "recv_meta", "y"):
+            _check_heap_tensor(heap, getattr(bufs, name), name)
+        if state is None:
+            state = torch.zeros(_ext.STEP_STATE_WORDS, dtype=torch.int32, device=heap.device)
+        self.heap, self.bufs, self.grid, self.threads, self.state = heap, bufs, grid, threads, state
+        self._keep = (x, topk_idx, topk_w, out, n_local, step_meta)
+        a = _ext.McbA2AStepArgs()
+        a.x, a.topk_idx, a.topk_w, a.out = x.data_ptr(), topk_idx.data_ptr(), _ext.ptr(topk_w), out.data_ptr()
+        a.n_local = n_local.data_ptr()
+        a.recv_x_off, a.x_par_stride = bufs.recv_x.offset, bufs.recv_x.nbytes // 2
+        if bufs.recv_scale is not None:
+            a.recv_scale_off, a.scale_par_stride = bufs.recv_scale.offset, bufs.recv_scale.nbytes // 2
+        a.recv_meta_off, a.meta_par_stride = bufs.recv_meta.offset, bufs.recv_meta.nbytes // 2
+        a.y_off, a.y_par_stride = bufs.y.offset, bufs.y.nbytes // 2
+        a.meta_row_bytes, a.hidden, a.topk, a.num_experts = bufs.meta_row_bytes, bufs.hidden, bufs.topk, int(num_experts)
+        a.cap, a.fp8, a.num_layers = bufs.cap, int(bufs.fp8), int(num_layers)
+        a.step_meta, a.counts_off, a.state = step_meta.data_ptr(), heap.a2a_counts_off, state.data_ptr()
+        self.args = a
+
+    def launch(self, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        _ext.check(lib.mcb_launch_a2a_step(C.byref(self.heap.ctx()), C.byref(self.args), self.grid, self.threads,
+                                           int(pdl), _ext.stream_handle(stream)), "a2a_step")
+
+
 def a2a_decode_step(heap, d: A2ADispatchPlan, c: A2ACombinePlan, num_layers: int, pdl: bool = False, stream=None):
     lib = _ext.require()
     heap.level_launch_counters(_ext.SITE_A2A_COMBINE, d.grid)

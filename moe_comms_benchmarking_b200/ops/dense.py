@@ -207,7 +207,11 @@ class DenseStepPlan:
                  cap: int, num_layers: int, grid: int = DEFAULT_GRID, threads: int = DEFAULT_THREADS,
                  agv_ll_stage: HeapTensor | None = None, rsv_ll_stage: HeapTensor | None = None, ll_rows: int = 0,
                  groups: int = 1, group_min_bytes: int = 256 << 10, state: torch.Tensor | None = None,
-                 credits: HeapTensor | None = None, check_errors: torch.Tensor | None = None, delay_ns: int = 0, delay_every: int = 1):
+                 credits: HeapTensor | None = None, check_errors: torch.Tensor | None = None, delay_ns: int = 0, delay_every: int = 1,
+                 fp8_hidden: int = 0):
+        """``fp8_hidden`` = H > 0 dispatches the hidden rows as 1 x 128 block-scaled e4m3: ``srcs[0]`` stays the
+        bf16 ``[cap, H]`` input, ``dsts[0]`` is ``[2, cap * world, H]`` uint8, and a fourth pair
+        ``(dsts[3], None)`` receives the fp32 scales ``[2, cap * world, H / 128]``."""
         if not (1 <= len(srcs) <= _ext.MAX_TENSORS) or len(srcs) != len(dsts):
             raise ValueError(f"need 1..{_ext.MAX_TENSORS} (dst, src) pairs")
         _check_grid(grid, threads)
@@ -227,18 +231,29 @@ class DenseStepPlan:
         self._keep = (list(dsts), list(srcs), out, rsv, n_local, step_meta, agv_ll_stage, rsv_ll_stage)
         a = _ext.McbDenseStepArgs()
         gcap = cap * heap.world
+        if fp8_hidden:
+            if fp8_hidden % 128 or len(srcs) != 4 or srcs[3] is not None or check_errors is not None:
+                raise ValueError("fp8 dispatch: hidden must be a multiple of 128 and the tensors "
+                                 "(hidden, routing, probs, scales) with no source for the scales")
+            if srcs[0].dtype != torch.bfloat16 or srcs[0].shape[1] != fp8_hidden or dsts[0].tensor.dtype != torch.uint8 \
+                    or dsts[3].tensor.dtype != torch.float32 or dsts[3].tensor.shape[2] != fp8_hidden // 128:
+                raise ValueError("fp8 dispatch: bf16 [cap, H] source, uint8 [2, rows, H] and fp32 [2, rows, H/128] gathered buffers")
         for i, (d, s) in enumerate(zip(dsts, srcs)):
-            rb = _row_bytes(s)
+            quant = bool(fp8_hidden) and i in (0, 3)
+            rb = (fp8_hidden if i == 0 else fp8_hidden // 128 * 4) if quant else _row_bytes(s)
             _check_heap_tensor(heap, d, f"dense_step dst[{i}]")
             if rb % 4:
                 raise ValueError(f"row of tensor {i} is {rb} bytes; must be a multiple of 4")
-            if d.tensor.dtype != s.dtype or d.tensor.dim() != 3 or d.tensor.shape[0] != 2 or d.tensor.shape[2] != s.shape[1]:
-                raise ValueError(f"tensor {i}: gathered buffer must be [2, cap * world, cols] of the source dtype")
-            if s.shape[0] < cap or d.tensor.shape[1] < gcap:
-                raise ValueError(f"tensor {i}: buffers smaller than the capacity")
-            if s.data_ptr() % 16:
-                raise ValueError(f"tensor {i}: source is not 16-byte aligned")
-            a.src[i], a.dst_off[i], a.row_bytes[i] = s.data_ptr(), d.offset, rb
+            if d.tensor.dim() != 3 or d.tensor.shape[0] != 2 or d.tensor.shape[1] < gcap:
+                raise ValueError(f"tensor {i}: gathered buffer must be [2, >= cap * world, cols]")
+            if not quant and (d.tensor.dtype != s.dtype or d.tensor.shape[2] != s.shape[1]):
+                raise ValueError(f"tensor {i}: gathered buffer must have the source's dtype and columns")
+            if s is not None:
+                if s.shape[0] < cap:
+                    raise ValueError(f"tensor {i}: source smaller than the capacity")
+                if s.data_ptr() % 16:
+                    raise ValueError(f"tensor {i}: source is not 16-byte aligned")
+            a.src[i], a.dst_off[i], a.row_bytes[i] = (s.data_ptr() if s is not None else 0), d.offset, rb
             a.dst_par_stride[i] = d.tensor.shape[1] * rb
             if a.dst_par_stride[i] % 16:
                 raise ValueError(f"tensor {i}: parity stride is not 16-byte aligned")
@@ -251,9 +266,10 @@ class DenseStepPlan:
         a.num_tensors, a.cap, a.num_layers = len(srcs), int(cap), int(num_layers)
         a.rsv_dtype = 1 if out.dtype == torch.float32 else 0
         a.out, a.rsv_off, a.rsv_row_bytes = out.data_ptr(), rsv.offset, rrb
+        rbs = [int(a.row_bytes[i]) for i in range(len(srcs))]
         if ll_rows > 0 and agv_ll_stage is not None and rsv_ll_stage is not None and out.dtype == torch.bfloat16 \
-                and all(_row_bytes(s) % 8 == 0 for s in srcs):
-            need_a = agv_ll_stage_bytes(ll_rows, [_row_bytes(s) for s in srcs])
+                and all(rb % 8 == 0 for rb in rbs):
+            need_a = agv_ll_stage_bytes(ll_rows, rbs)
             need_r = rsv_ll_stage_bytes(heap.world, ll_rows, cap, rrb)
             _check_heap_tensor(heap, agv_ll_stage, "dense_step packet staging (gather)")
             _check_heap_tensor(heap, rsv_ll_stage, "dense_step packet staging (reduce)")
@@ -265,7 +281,7 @@ class DenseStepPlan:
             a.ll_rows, a.ll_src_rows = int(ll_rows), min(int(cap), int(ll_rows))
             a.agv_ll_off, a.rsv_ll_off, a.credit_off = agv_ll_stage.offset, rsv_ll_stage.offset, credits.offset
             self._keep += (credits,)
-        a.groups, a.group_min_bytes = int(groups), int(group_min_bytes)
+        a.groups, a.group_min_bytes, a.fp8_hidden = int(groups), int(group_min_bytes), int(fp8_hidden)
         a.n_local, a.step_meta = n_local.data_ptr(), step_meta.data_ptr()
         a.counts_off, a.state = heap.step_counts_off, state.data_ptr()
         if check_errors is not None:

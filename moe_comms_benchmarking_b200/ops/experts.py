@@ -24,23 +24,61 @@ BLOCK_M = 128
 
 
 class ExpertWeights:
-    """bf16 weights of this rank's experts: ``w_gate_up [E_loc, 2*I, H]`` (gate rows, then up
-    rows) and ``w_down [E_loc, H, I]``, plus their TMA tensor maps."""
+    """bf16 weights of this rank's experts and their TMA tensor maps.
 
-    def __init__(self, num_local_experts: int, hidden: int, intermediate: int, device, seed: int = 0, std: float = 0.02):
+    ``w_down`` is ``[E_loc, H, I]``.  The gate/up matrix exists in one of two layouts of the same
+    values (random N(0, std^2), generated as ``[E_loc, 2*I, H]`` with the gate rows first):
+
+    * ``layout="interleaved"`` (default): row ``2i`` is gate row ``i`` and row ``2i + 1`` is up row
+      ``i``, which is what the weights-as-M FFN kernel streams (a 128-row block then holds 64
+      finished activations);
+    * ``layout="split"``: gate rows then up rows, for the tokens-as-rows GEMM kernels.
+
+    ``w_gate_up`` always returns the split layout (computed on demand from the interleaved one),
+    which is what the CPU oracle takes."""
+
+    def __init__(self, num_local_experts: int, hidden: int, intermediate: int, device, seed: int = 0, std: float = 0.02,
+                 layout: str = "interleaved"):
         if hidden % 256 or intermediate % 128:
             raise ValueError("hidden must be a multiple of 256 and intermediate a multiple of 128")
+        if layout not in ("interleaved", "split"):
+            raise ValueError(f"unknown gate/up layout {layout!r}")
         g = torch.Generator(device=device).manual_seed(seed)
         self.num_local_experts, self.hidden, self.intermediate = num_local_experts, hidden, intermediate
-        self.w_gate_up = (torch.randn(num_local_experts, 2 * intermediate, hidden, device=device, generator=g,
-                                      dtype=torch.float32) * std).to(torch.bfloat16)
+        self.layout = layout
+        split = (torch.randn(num_local_experts, 2 * intermediate, hidden, device=device, generator=g,
+                             dtype=torch.float32) * std).to(torch.bfloat16)
         self.w_down = (torch.randn(num_local_experts, hidden, intermediate, device=device, generator=g,
                                    dtype=torch.float32) * std).to(torch.bfloat16)
-        self.map_gate_up = make_weight_tmap(self.w_gate_up.view(-1, hidden))
+        if layout == "interleaved":
+            self.w1 = self.interleave(split)
+            del split
+        else:
+            self.w1 = split
+        self.map_w1 = make_weight_tmap(self.w1.view(-1, hidden))
         self.map_down = make_weight_tmap(self.w_down.view(-1, intermediate))
 
+    @staticmethod
+    def interleave(split: torch.Tensor) -> torch.Tensor:
+        """``[E, 2I, H]`` gate rows then up rows -> row 2i = gate i, row 2i + 1 = up i."""
+        E, two_i, H = split.shape
+        return split.view(E, 2, two_i // 2, H).transpose(1, 2).contiguous().view(E, two_i, H)
+
+    @property
+    def w_gate_up(self) -> torch.Tensor:
+        if self.layout == "split":
+            return self.w1
+        E, two_i, H = self.w1.shape
+        return self.w1.view(E, two_i // 2, 2, H).transpose(1, 2).contiguous().view(E, two_i, H)
+
+    @property
+    def map_gate_up(self):
+        if self.layout != "split":
+            raise ValueError("the tokens-as-rows GEMM kernels need ExpertWeights(layout='split')")
+        return self.map_w1
+
     def bytes(self) -> int:
-        return (self.w_gate_up.numel() + self.w_down.numel()) * 2
+        return (self.w1.numel() + self.w_down.numel()) * 2
 
 
 def make_weight_tmap(w2d: torch.Tensor):
@@ -74,6 +112,8 @@ class RouteBuffers:
         self.tile_rows = torch.zeros(self.max_tiles, **i32)
         self.num_m_tiles = torch.zeros(1, **i32)
         self.sync = torch.zeros(4, **i32)
+        self.max_rows = torch.zeros(1, **i32)            # largest pair count of one expert
+        self.ffn_done = torch.zeros(num_local_experts, **i32)   # gate/up blocks finished per expert (fused FFN)
 
 
 class RoutePlan:
@@ -93,7 +133,7 @@ class RoutePlan:
         a.topk_idx, a.topk_w, a.num_tokens = topk_idx.data_ptr(), _ext.ptr(topk_w), num_tokens.data_ptr()
         a.topk, a.expert_begin, a.num_local_experts, a.max_tokens = bufs.topk, int(expert_begin), bufs.E, bufs.max_tokens
         for f in ("expert_count", "expert_cursor", "expert_offset", "pair_token", "pair_prob", "pair_pos",
-                  "tile_expert", "tile_row0", "tile_rows", "num_m_tiles", "sync"):
+                  "tile_expert", "tile_row0", "tile_rows", "num_m_tiles", "sync", "max_rows", "ffn_done"):
             setattr(a, f, getattr(bufs, f).data_ptr())
         a.max_pairs, a.max_tiles = bufs.max_pairs, bufs.max_tiles
         a.status, a.timeout_ns = _ext.ptr(status), int(timeout_s * 1e9)
@@ -201,3 +241,93 @@ class DispatchRouteFc1Plan:
                                                      C.byref(self.heap.ctx()), C.byref(self.agv.args),
                                                      C.byref(self.route.args), self.grid, int(pdl),
                                                      _ext.stream_handle(stream)), "dispatch_route_fc1")
+
+
+def _aligned_layer_args(count: int):
+    """``count`` zeroed McbLayerArgs in 64-byte aligned host memory: (keep-alive buffer, address, stride)."""
+    stride = _ext.layer_args_size()
+    raw = (C.c_uint8 * (stride * count + 64))()
+    addr = (C.addressof(raw) + 63) & ~63
+    return raw, addr, stride
+
+
+class ExpertFfnPlan:
+    """Gate/up + SwiGLU + down over the pair lists of ``route`` as ONE persistent launch
+    (``expert_ffn_kernel``): weights are the M = 128 operand, an expert's tokens the small N."""
+
+    def __init__(self, weights: ExpertWeights, route: RouteBuffers, x: torch.Tensor, act: torch.Tensor, y: torch.Tensor,
+                 status: torch.Tensor | None = None, grid: int = NUM_SMS, timeout_s: float = 2.0):
+        H, I = weights.hidden, weights.intermediate
+        if weights.layout != "interleaved":
+            raise ValueError("the FFN kernel streams the interleaved gate/up layout")
+        for t, cols, what in ((x, H, "x"), (act, I, "act"), (y, H, "y")):
+            if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.shape[-1] != cols:
+                raise ValueError(f"{what} must be contiguous bf16 with {cols} columns")
+        if act.shape[0] < route.max_pairs or y.shape[0] < route.max_pairs:
+            raise ValueError("act and y must hold max_pairs rows")
+        if not (1 <= grid <= NUM_SMS):
+            raise ValueError("down blocks wait for gate/up blocks of other CTAs: grid <= number of SMs")
+        self.weights, self.grid = weights, grid
+        self._keep = (route, x, act, y, status)
+        a = _ext.McbFfnArgs()
+        a.x, a.x_row_bytes = x.data_ptr(), H * 2
+        a.pair_token, a.pair_prob = route.pair_token.data_ptr(), route.pair_prob.data_ptr()
+        a.expert_offset, a.max_rows = route.expert_offset.data_ptr(), route.max_rows.data_ptr()
+        a.act, a.y, a.ffn_done = act.data_ptr(), y.data_ptr(), route.ffn_done.data_ptr()
+        a.num_local_experts, a.hidden, a.intermediate = weights.num_local_experts, H, I
+        a.status, a.timeout_ns = _ext.ptr(status), int(timeout_s * 1e9)
+        self.args = a
+
+    def launch(self, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        _ext.check(lib.mcb_launch_expert_ffn(C.c_void_p(self.weights.map_w1[1]), C.c_void_p(self.weights.map_down[1]),
+                                             C.byref(self.args), self.grid, int(pdl), _ext.stream_handle(stream)),
+                   "expert_ffn")
+
+
+class MoeLayerPlan:
+    """One whole MoE layer per launch (``moe_layer_kernel``: dispatch, routing, experts, combine), for
+    one or several weight sets; ``launch(s)`` runs the layer with set ``s``, ``decode_step(n)`` issues the
+    count exchange and ``n`` layers natively (layer l uses set l % sets)."""
+
+    def __init__(self, heap: SymmetricHeap, agv, route: RoutePlan, ffns: list[ExpertFfnPlan], combine: ExpertCombinePlan,
+                 meta, grid: int = NUM_SMS):
+        if not (1 <= grid <= NUM_SMS):
+            raise ValueError("the layer kernel needs all its blocks resident at once: grid <= number of SMs")
+        self.heap, self.agv, self.route, self.ffns, self.combine, self.meta, self.grid = heap, agv, route, ffns, combine, meta, grid
+        self._raw, self._addr, self._stride = _aligned_layer_args(len(ffns))
+        self._ctx_version = None
+        self._fill()
+
+    def _fill(self):
+        ctx = self.heap.ctx()
+        for s, f in enumerate(self.ffns):
+            p = _ext.McbLayerArgs.from_address(self._addr + s * self._stride)
+            C.memmove(C.addressof(p.w1), f.weights.map_w1[1], 128)
+            C.memmove(C.addressof(p.w2), f.weights.map_down[1], 128)
+            C.memmove(C.addressof(p.ctx), C.addressof(ctx), C.sizeof(_ext.McbCtx))
+            C.memmove(C.addressof(p.agv), C.addressof(self.agv.args), C.sizeof(_ext.McbAgvArgs))
+            C.memmove(C.addressof(p.route), C.addressof(self.route.args), C.sizeof(_ext.McbRouteArgs))
+            C.memmove(C.addressof(p.ffn), C.addressof(f.args), C.sizeof(_ext.McbFfnArgs))
+            C.memmove(C.addressof(p.cmb), C.addressof(self.combine.args), C.sizeof(_ext.McbCombineArgs))
+        self._ctx_version = id(ctx)
+
+    def _sync_ctx(self):
+        if self._ctx_version != id(self.heap.ctx()):      # the heap's context was rebuilt (e.g. a new timeout)
+            self._fill()
+
+    def args(self, s: int = 0) -> "_ext.McbLayerArgs":
+        return _ext.McbLayerArgs.from_address(self._addr + s * self._stride)
+
+    def launch(self, s: int = 0, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        self._sync_ctx()
+        _ext.check(lib.mcb_launch_moe_layer(C.c_void_p(self._addr + s * self._stride), self.grid, int(pdl),
+                                            _ext.stream_handle(stream)), "moe_layer")
+
+    def decode_step(self, num_layers: int, pdl: bool = False, stream=None):
+        lib = _ext.require()
+        self._sync_ctx()
+        _ext.check(lib.mcb_moe_decode_step(C.byref(self.heap.ctx()), C.byref(self.meta.args), C.c_void_p(self._addr),
+                                           len(self.ffns), int(num_layers), self.grid, int(pdl),
+                                           _ext.stream_handle(stream)), "moe_decode_step")

@@ -12,7 +12,9 @@ import torch
 import torch.distributed as dist
 
 from ..config import Config
-from ..ops.a2a import A2ABuffers, A2ACombinePlan, A2ADispatchPlan, a2a_decode_step, dequant_e4m3_1x128
+from ..ops import _ext
+from ..ops.a2a import (A2ABuffers, A2ACombinePlan, A2ADispatchPlan, A2AStepBuffers, A2AStepPlan, a2a_decode_step,
+                       dequant_e4m3_1x128)
 from ..ops.dense import DEFAULT_GRID, DEFAULT_THREADS
 from .base import Dispatcher
 from .symm_heap import SymmetricHeap, required_bytes
@@ -23,7 +25,7 @@ class A2ADispatcher(Dispatcher):
 
     def __init__(self, cfg: Config, group, heap: SymmetricHeap | None = None, num_sms: int = DEFAULT_GRID,
                  threads: int = DEFAULT_THREADS, pdl: bool = True, fp8_dispatch: bool = False,
-                 transport: str = "auto", device=None):
+                 transport: str = "auto", persistent: bool = True, device=None):
         super().__init__(cfg, group, device)
         self.heap = heap
         self._own_heap = heap is None
@@ -32,11 +34,17 @@ class A2ADispatcher(Dispatcher):
         self.transport = transport
         if self.fp8:
             self.name = "a2a-fp8"
-        self.kernel_launches_per_step = lambda nl: 2 * nl
+        # persistent: a whole decode step is ONE kernel (token-indexed slots, one barrier per layer);
+        # otherwise 2 x layers launches of the dispatch / combine kernels with compacted slots and counts.
+        self.persistent = bool(persistent)
+        self.kernel_launches_per_step = lambda nl: 1 if self.persistent else 2 * nl
+        self._step_plans = {}
 
     @staticmethod
     def heap_specs(cfg: Config, fp8: bool = False):
-        return A2ABuffers.specs(cfg.ep_size, max(cfg.per_rank_cap, 1), cfg.hidden, cfg.topk, fp8)
+        cap = max(cfg.per_rank_cap, 1)
+        return (A2ABuffers.specs(cfg.ep_size, cap, cfg.hidden, cfg.topk, fp8)
+                + A2AStepBuffers.specs(cfg.ep_size, cap, cfg.hidden, cfg.topk, fp8))
 
     def build(self):
         cfg, dev = self.cfg, self.device
@@ -46,6 +54,10 @@ class A2ADispatcher(Dispatcher):
             self.heap = SymmetricHeap(self.group, required_bytes(self.heap_specs(cfg, self.fp8)), dev,
                                       transport=self.transport)
         self.bufs = A2ABuffers(self.heap, cap, H, K, self.fp8, prefix="a2a8" if self.fp8 else "a2a")
+        self.step_bufs = A2AStepBuffers(self.heap, cap, H, K, self.fp8, prefix="a2as8" if self.fp8 else "a2as")
+        self.step_metadata = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.step_state = torch.zeros(_ext.STEP_STATE_WORDS, dtype=torch.int32, device=dev)
+        self.heap.register_reset_hook(self.step_state.zero_)
         self.in_hidden = torch.zeros(cap, H, dtype=torch.bfloat16, device=dev)
         self.in_routing = torch.zeros(cap, K, dtype=torch.int64, device=dev)
         self.in_probs = torch.zeros(cap, K, dtype=torch.float32, device=dev)
@@ -54,6 +66,7 @@ class A2ADispatcher(Dispatcher):
         self.local_tokens = 0
         if self.fp8:
             self.bufs.y.tensor.normal_()    # timed combine reduces valid data
+            self.step_bufs.y.tensor.normal_()
         self._make_plans()
         torch.cuda.synchronize()
         dist.barrier(self.group)
@@ -65,6 +78,16 @@ class A2ADispatcher(Dispatcher):
                                              threads=self.threads)
         self.combine_plan = A2ACombinePlan(self.heap, self.bufs, self.out_buf, self.n_local, grid=self.num_sms,
                                            threads=self.threads)
+        self._step_plans = {}
+
+    def _step_plan(self, num_layers: int) -> A2AStepPlan:
+        plan = self._step_plans.get(num_layers)
+        if plan is None:
+            plan = A2AStepPlan(self.heap, self.step_bufs, self.in_hidden, self.in_routing, self.in_probs, self.out_buf,
+                               self.n_local, self.step_metadata, self.cfg.num_experts, num_layers, grid=self.num_sms,
+                               threads=self.threads, state=self.step_state)
+            self._step_plans[num_layers] = plan
+        return plan
 
     def set_num_sms(self, num_sms: int):
         self.num_sms = int(num_sms)
@@ -93,7 +116,10 @@ class A2ADispatcher(Dispatcher):
         self.combine_plan.launch(self.pdl)
 
     def decode_step(self, num_layers: int):
-        a2a_decode_step(self.heap, self.dispatch_plan, self.combine_plan, num_layers, self.pdl)
+        if self.persistent:
+            self._step_plan(num_layers).launch(self.pdl)
+        else:
+            a2a_decode_step(self.heap, self.dispatch_plan, self.combine_plan, num_layers, self.pdl)
 
     def check_health(self):
         self.heap.check_status()
@@ -128,12 +154,79 @@ class A2ADispatcher(Dispatcher):
         self._sync_all()
         return self.out
 
+    def _validate_step_kernel(self, B: int):
+        """The persistent step kernel on tokens every rank can regenerate: what each source sent here
+        (rows, packed routing, stamps) and the combined output m * x."""
+        w, rank, dev = self.cfg.ep_size, self.cfg.rank, self.device
+        H, K, E, sb = self.cfg.hidden, self.cfg.topk, self.cfg.num_experts, self.step_bufs
+        epr = E // w
+        counts = self._validation_counts(B)
+        offs = [sum(counts[:r]) for r in range(w)]
+        gen = torch.Generator(device=dev).manual_seed(880801 + B)          # same on all ranks
+        full_x = torch.randn(B, H, generator=gen, device=dev).to(torch.bfloat16)
+        full_i = torch.stack([torch.randperm(E, generator=gen, device=dev)[:K] for _ in range(B)])
+        full_w = torch.rand(B, K, generator=gen, device=dev)
+        n, off = counts[rank], offs[rank]
+        self.setup_batch(full_x[off:off + n], full_i[off:off + n], full_w[off:off + n])
+        ok, why = True, []
+        for nl in (3, 2):
+            sb.recv_meta.tensor.zero_()
+            self._sync_all()
+            self.decode_step(nl)
+            self._sync_all()
+            par, stamp = int(self.step_metadata[5]), int(self.step_metadata[7])
+            for s in range(w):
+                c = counts[s]
+                if not c:
+                    continue
+                st, tok, ids, wts = sb.meta_fields(par, s, c)
+                here = ((full_i[offs[s]:offs[s] + c] // epr) == rank).any(dim=1)
+                if not torch.equal(st == stamp, here):
+                    ok = False; why.append(f"stamps of source {s}")
+                    continue
+                sel = here.nonzero().flatten()
+                if sel.numel() == 0:
+                    continue
+                good = (torch.equal(tok[sel].long(), sel) and torch.equal(ids[sel].long(), full_i[offs[s] + sel])
+                        and torch.equal(wts[sel], full_w[offs[s] + sel]))
+                want = full_x[offs[s] + sel]
+                if self.fp8:
+                    got = dequant_e4m3_1x128(sb.recv_x.tensor[par, s][sel], sb.recv_scale.tensor[par, s][sel]).float()
+                    good = good and bool(((got - want.float()).abs() <= 0.07 * want.float().abs() + 0.02).all())
+                else:
+                    good = good and torch.equal(sb.recv_x.tensor[par, s][sel], want)
+                if not good:
+                    ok = False; why.append(f"rows of source {s}")
+            if self.fp8:
+                # identity expert on the host: expert outputs = the dequantised received rows; one more step
+                for s in range(w):
+                    if counts[s]:
+                        sb.y.tensor[:, s, :counts[s]] = dequant_e4m3_1x128(sb.recv_x.tensor[par, s, :counts[s]],
+                                                                          sb.recv_scale.tensor[par, s, :counts[s]])
+                self._sync_all()
+                self.decode_step(2)
+                self._sync_all()
+            if n:
+                m = torch.tensor([torch.unique(full_i[off + t] // epr).numel() for t in range(n)], device=dev,
+                                 dtype=torch.float32).view(n, 1)
+                ref = m * full_x[off:off + n].float()
+                err = float((self.out.float() - ref).abs().max()) / (float(ref.abs().max()) + 1e-6)
+                if err >= (0.08 if self.fp8 else 0.02):
+                    ok = False; why.append(f"combine off by {100 * err:.2f}%")
+        return ok, ("received rows, packed routing and stamps match every source; combine == m*x (steps of 3 and 2 layers)"
+                    if ok else "; ".join(why))
+
     def validate(self):
         w, rank, dev = self.cfg.ep_size, self.cfg.rank, self.device
         H, K, E = self.cfg.hidden, self.cfg.topk, self.cfg.num_experts
         epr = E // w
         tol = 0.08 if self.fp8 else 0.05
         results = []
+        if self.persistent:
+            for B in (w * 2, 1):
+                if max(self._validation_counts(B)) <= self.cap:
+                    ok, detail = self._validate_step_kernel(B)
+                    results.append((f"{self.name} step kernel       B={B:<4d}", bool(ok), detail))
         for B in (w * 2, 1):
             counts = self._validation_counts(B)
             if max(counts) > self.cap:

@@ -43,11 +43,20 @@ class DenseDispatcher(Dispatcher):
     def __init__(self, cfg: Config, group, heap: SymmetricHeap | None = None, num_sms: int = DEFAULT_GRID,
                  threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto",
                  combine_dtype=torch.bfloat16, ll_rows: int = -1, persistent: bool = True, groups: int = 1,
-                 group_min_bytes: int = 256 << 10, device=None):
+                 group_min_bytes: int = 256 << 10, fp8_dispatch: bool = False, device=None):
         super().__init__(cfg, group, device)
         self.heap = heap
         self._own_heap = heap is None
         self.persistent = bool(persistent)
+        # 1 x 128 block-scaled e4m3 dispatch of the hidden rows (quantised inside the step kernel's
+        # push, scales gathered as a fourth tensor); the combine stays bf16.
+        self.fp8 = bool(fp8_dispatch)
+        if self.fp8:
+            if not self.persistent:
+                raise ValueError("fp8 dispatch is part of the persistent step kernel")
+            if cfg.hidden % 256:
+                raise ValueError("fp8 dispatch needs a hidden size that is a multiple of 256")
+            self.name = "dense-fp8"
         self.num_sms = self._grid_for(cfg, num_sms)
         self.threads = int(threads)
         self.pdl = bool(pdl)
@@ -63,19 +72,21 @@ class DenseDispatcher(Dispatcher):
         self._step_plans = {}
 
     @staticmethod
-    def _ll_bytes(cfg: Config, ll_rows: int):
+    def _ll_bytes(cfg: Config, ll_rows: int, fp8: bool = False):
         H, K = cfg.hidden, cfg.topk
         ll_rows = resolve_ll_rows(cfg, ll_rows)
-        return (agv_ll_stage_bytes(ll_rows, [H * 2, K * 8, K * 4]),
+        rows = [H, K * 8, K * 4, H // 128 * 4] if fp8 else [H * 2, K * 8, K * 4]
+        return (agv_ll_stage_bytes(ll_rows, rows),
                 rsv_ll_stage_bytes(cfg.ep_size, ll_rows, max(cfg.per_rank_cap, 1), H * 2))
 
     @staticmethod
-    def heap_specs(cfg: Config, combine_dtype=torch.bfloat16, ll_rows: int = -1):
+    def heap_specs(cfg: Config, combine_dtype=torch.bfloat16, ll_rows: int = -1, fp8: bool = False):
         g, H, K = max(cfg.global_cap, 1), cfg.hidden, cfg.topk
-        a, r = DenseDispatcher._ll_bytes(cfg, ll_rows)
-        return [([2, g, H], torch.bfloat16), ([2, g, K], torch.int64), ([2, g, K], torch.float32),
-                ([g, H], combine_dtype), ([max(a, 16)], torch.uint8), ([max(r, 16)], torch.uint8),
-                ([step_credit_bytes()], torch.uint8)]
+        a, r = DenseDispatcher._ll_bytes(cfg, ll_rows, fp8)
+        hidden = [([2, g, H], torch.uint8), ([2, g, H // 128], torch.float32)] if fp8 else [([2, g, H], torch.bfloat16)]
+        return hidden + [([2, g, K], torch.int64), ([2, g, K], torch.float32),
+                         ([g, H], combine_dtype), ([max(a, 16)], torch.uint8), ([max(r, 16)], torch.uint8),
+                         ([step_credit_bytes()], torch.uint8)]
 
     def build(self):
         cfg, dev = self.cfg, self.device
@@ -83,18 +94,19 @@ class DenseDispatcher(Dispatcher):
         self.cap = cap
         if self.heap is None:
             self.heap = SymmetricHeap(self.group,
-                                      required_bytes(self.heap_specs(cfg, self.combine_dtype, self.ll_rows)), dev,
+                                      required_bytes(self.heap_specs(cfg, self.combine_dtype, self.ll_rows, self.fp8)), dev,
                                       transport=self.transport)
         h = self.heap
         # Gathered rows, double buffered by layer parity for the persistent step kernel; the
         # stand-alone dispatch and the validation use parity 0.
-        self.agv2_h = h.alloc("ep_agv_h", [2, g, H], torch.bfloat16)
+        self.agv2_h = h.alloc("ep_agv_h", [2, g, H], torch.uint8 if self.fp8 else torch.bfloat16)
+        self.agv2_s = h.alloc("ep_agv_s", [2, g, H // 128], torch.float32) if self.fp8 else None
         self.agv2_r = h.alloc("ep_agv_r", [2, g, K], torch.int64)
         self.agv2_p = h.alloc("ep_agv_p", [2, g, K], torch.float32)
         self.agv_h, self.agv_r, self.agv_p = (HeapTensor(t.tensor[0], t.offset, t.nbytes // 2)
                                               for t in (self.agv2_h, self.agv2_r, self.agv2_p))
         self.rsv = h.alloc("ep_rsv", [g, H], self.combine_dtype)
-        a_bytes, r_bytes = self._ll_bytes(cfg, self.ll_rows)
+        a_bytes, r_bytes = self._ll_bytes(cfg, self.ll_rows, self.fp8)
         self.ll_agv = h.alloc("ep_ll_agv", [max(a_bytes, 16)], torch.uint8)
         self.ll_rsv = h.alloc("ep_ll_rsv", [max(r_bytes, 16)], torch.uint8)
         self.step_credits = h.alloc("ep_step_credit", [step_credit_bytes()], torch.uint8)
@@ -117,6 +129,10 @@ class DenseDispatcher(Dispatcher):
 
     def _make_plans(self):
         h = self.heap
+        self._step_plans = {}
+        if self.fp8:        # the quantised dispatch exists only inside the step kernel
+            self.meta_plan = self.agv_plan = self.rsv_plan = None
+            return
         self.meta_plan = MetadataPlan(h, self.n_local, self.step_metadata, self.cap)
         self.agv_plan = AllGatherVPlan(h, [self.agv_h, self.agv_r, self.agv_p],
                                        [self.in_hidden, self.in_routing, self.in_probs], self.n_local,
@@ -128,16 +144,19 @@ class DenseDispatcher(Dispatcher):
         self._step_plans = {}
 
     def _step_plan(self, num_layers: int, **check) -> DenseStepPlan:
-        plan = None if check else self._step_plans.get(num_layers)
+        cached = not check            # plans of the self-checking build are made per use
+        plan = self._step_plans.get(num_layers) if cached else None
         if plan is None:
-            plan = DenseStepPlan(self.heap, [self.agv2_h, self.agv2_r, self.agv2_p],
-                                 [self.in_hidden, self.in_routing, self.in_probs], self.out_buf, self.rsv,
+            dsts, srcs = [self.agv2_h, self.agv2_r, self.agv2_p], [self.in_hidden, self.in_routing, self.in_probs]
+            if self.fp8:
+                dsts, srcs, check = dsts + [self.agv2_s], srcs + [None], dict(check, fp8_hidden=self.cfg.hidden)
+            plan = DenseStepPlan(self.heap, dsts, srcs, self.out_buf, self.rsv,
                                  self.n_local, self.step_metadata, self.cap, num_layers, grid=self.num_sms,
                                  threads=self.threads, agv_ll_stage=self.ll_agv, rsv_ll_stage=self.ll_rsv,
                                  ll_rows=self.ll_rows, credits=self.step_credits,
                                  groups=self.groups if self.num_sms <= DEFAULT_GRID else 1,
                                  group_min_bytes=self.group_min_bytes, state=self.step_state, **check)
-            if not check:
+            if cached:
                 self._step_plans[num_layers] = plan
         return plan
 
@@ -211,14 +230,19 @@ class DenseDispatcher(Dispatcher):
         return self.out_buf[:self.local_tokens]
 
     # -- timed ops -----------------------------------------------------------------------------------
+    def _standalone(self, plan):
+        if plan is None:
+            raise RuntimeError("with fp8 dispatch the dense path runs as whole decode steps only (decode_step)")
+        return plan
+
     def metadata(self):
-        self.meta_plan.launch(self.pdl)
+        self._standalone(self.meta_plan).launch(self.pdl)
 
     def dispatch(self):
-        self.agv_plan.launch(self.pdl)
+        self._standalone(self.agv_plan).launch(self.pdl)
 
     def combine(self):
-        self.rsv_plan.launch(self.pdl)
+        self._standalone(self.rsv_plan).launch(self.pdl)
 
     def decode_step(self, num_layers: int):
         if self.persistent:
@@ -228,9 +252,19 @@ class DenseDispatcher(Dispatcher):
 
     def gathered(self):
         """(hidden, routing, probs) views of the rows gathered by the LAST decode step
-        (host-synchronising: reads the parity word the step kernel wrote)."""
+        (host-synchronising: reads the parity word the step kernel wrote).  With fp8 dispatch the first
+        entry is the pair (e4m3 bytes, fp32 scales)."""
         par = int(self.step_metadata[5].item()) if self.persistent else 0
-        return self.agv2_h.tensor[par], self.agv2_r.tensor[par], self.agv2_p.tensor[par]
+        hid = (self.agv2_h.tensor[par], self.agv2_s.tensor[par]) if self.fp8 else self.agv2_h.tensor[par]
+        return hid, self.agv2_r.tensor[par], self.agv2_p.tensor[par]
+
+    def gathered_hidden_bf16(self, rows: int):
+        """The first ``rows`` gathered hidden rows as bf16 (dequantised when the dispatch was fp8)."""
+        hid = self.gathered()[0]
+        if not self.fp8:
+            return hid[:rows]
+        from ..ops.a2a import dequant_e4m3_1x128
+        return dequant_e4m3_1x128(hid[0][:rows], hid[1][:rows])
 
     def check_health(self):
         self.heap.check_status()
@@ -246,6 +280,8 @@ class DenseDispatcher(Dispatcher):
         w, rank, dev = self.cfg.ep_size, self.cfg.rank, self.device
         H, K, E, g = self.cfg.hidden, self.cfg.topk, self.cfg.num_experts, max(self.cfg.global_cap, 1)
         results = []
+        if self.fp8:
+            return self._validate_fp8()
         for B in (w * 2, 1):
             counts = self._validation_counts(B)
             if max(counts) > self.cap:
@@ -303,12 +339,77 @@ class DenseDispatcher(Dispatcher):
             results.append(("dense device status", False, str(e)))
         return results
 
+    def _validate_fp8(self):
+        """Quantised dispatch: gathered routing/probs bit-exact, scales == amax / 448 per 128 values,
+        dequantised rows within e4m3 rounding of the inputs, combine == world * rsv; B = 2*ep (and a step
+        of 3 layers, then 2) and B = 1."""
+        from ..ops import oracle
+        w, rank, dev = self.cfg.ep_size, self.cfg.rank, self.device
+        H, K, E = self.cfg.hidden, self.cfg.topk, self.cfg.num_experts
+        results = []
+        for B in (w * 2, 1):
+            counts = self._validation_counts(B)
+            if max(counts) > self.cap:
+                continue
+            n, off, valid = counts[rank], sum(counts[:rank]), sum(counts)
+            gen = torch.Generator(device=dev).manual_seed(20260701 + B)
+            full_h = torch.randn(valid, H, generator=gen, device=dev).to(torch.bfloat16)
+            full_h[0, :128] = 0                      # an all-zero block: scale 1, values 0
+            full_r = torch.stack([torch.randperm(E, generator=gen, device=dev)[:K] for _ in range(valid)])
+            full_p = torch.rand(valid, K, generator=gen, device=dev)
+            rsv_full = torch.randn(valid, H, generator=gen, device=dev).to(self.combine_dtype)
+            self.setup_batch(full_h[off:off + n], full_r[off:off + n], full_p[off:off + n])
+            self.rsv.tensor[:valid] = rsv_full
+            for nl in (3, 2):
+                for t in (self.agv2_h, self.agv2_r, self.agv2_p, self.agv2_s):
+                    t.tensor.zero_()
+                self.out_buf.zero_()
+                self._sync_all()
+                self.decode_step(nl)
+                self._sync_all()
+                meta = self.step_metadata.tolist()
+                (q, sc), gr, gp = self.gathered()
+                _, s_ref = oracle.quant_e4m3_1x128(full_h.float().cpu())
+                back = oracle.dequant_e4m3_1x128(q[:valid].cpu().view(torch.float8_e4m3fn), sc[:valid].cpu())
+                want = full_h.float().cpu()
+                ok = (meta[:3] == [valid, off, max(counts)] and torch.equal(gr[:valid], full_r)
+                      and torch.equal(gp[:valid], full_p)
+                      and torch.allclose(sc[:valid].cpu(), s_ref, rtol=1e-6, atol=0)
+                      and bool(((back - want).abs() <= 0.0625 * want.abs()
+                                + 2e-3 * sc[:valid].cpu().repeat_interleave(128, dim=1)).all())
+                      and (n == 0 or torch.allclose(self.out.float(), w * rsv_full[off:off + n].float(),
+                                                    rtol=2e-2, atol=2e-2)))
+                results.append((f"dense-fp8 step kernel B={B:<4d}", bool(ok),
+                                f"{nl} layers: e4m3 rows + fp32 scales match the 1x128 quantisation of the inputs, "
+                                f"routing/probs bit-exact, output == world*rsv; mode={'packets' if meta[6] else 'barrier'}"))
+        try:
+            self.check_health()
+        except Exception as e:
+            results.append(("dense-fp8 device status", False, str(e)))
+        return results
+
     def functional_roundtrip(self, hidden, topk_idx):
         """dispatch -> masked identity expert -> combine; returns ``[n, H]`` = m * x
         (bench_nvls.py:174-199)."""
         w, rank = self.cfg.ep_size, self.cfg.rank
         epr = self.cfg.num_experts // w
         n = hidden.shape[0]
+        if self.fp8:
+            # The quantised dispatch lives in the step kernel: one layer to gather, the masked identity
+            # expert on the host, one more layer whose combine then reduces the masked rows.
+            self.setup_batch(hidden, topk_idx, torch.ones(n, self.cfg.topk, device=self.device))
+            self.rsv.tensor.zero_()
+            self._sync_all()
+            self.decode_step(1)
+            self._sync_all()
+            valid = int(self.step_metadata[0].item())
+            gh, gr = self.gathered_hidden_bf16(valid), self.gathered()[1][:valid]
+            local = ((gr >= rank * epr) & (gr < (rank + 1) * epr)).any(dim=1, keepdim=True)
+            self.rsv.tensor[:valid] = torch.where(local, gh.float(), torch.zeros((), device=self.device)).to(self.combine_dtype)
+            self._sync_all()
+            self.decode_step(1)
+            self._sync_all()
+            return self.out
         self.setup_batch(hidden, topk_idx, torch.ones(n, self.cfg.topk, device=self.device))
         self.metadata()
         self.dispatch()

@@ -15,7 +15,8 @@ import ctypes as C
 import torch
 
 from ..ops import _ext
-from .symm_heap import ALIGN, COUNTS_BYTES, FLAGS_BYTES, RESERVED_BYTES, DeviceStatusError, HeapTensor, _align
+from .symm_heap import (ALIGN, COUNTS_BYTES, FLAGS_BYTES, RESERVED_BYTES, STEP_COUNTS_BYTES, DeviceStatusError,
+                        HeapTensor, _align)
 
 
 def _to_device(structs, device) -> torch.Tensor:
@@ -50,6 +51,9 @@ class EmuWorld:
         self.counts_off = FLAGS_BYTES
         self._site_grid = {}
         self.step_counts_off = FLAGS_BYTES + COUNTS_BYTES
+        self.a2a_counts_off = FLAGS_BYTES + COUNTS_BYTES + STEP_COUNTS_BYTES
+        self.a2a_state = [torch.zeros(_ext.STEP_STATE_WORDS, dtype=torch.int32, device=self.device)
+                          for _ in range(world)]
         self.step_state = [torch.zeros(_ext.STEP_STATE_WORDS, dtype=torch.int32, device=self.device)
                            for _ in range(world)]
 
@@ -141,17 +145,21 @@ class EmuWorld:
 
     def dense_step(self, dsts, srcs, outs, rsv, n_locals, step_metas, cap, num_layers, grid=4, threads=256,
                    agv_ll_stage=None, rsv_ll_stage=None, ll_rows=0, groups=1, group_min_bytes=0,
-                   check_errors=None, delays_ns=None, delay_every=1):
+                   check_errors=None, delays_ns=None, delay_every=1, fp8_hidden=0):
         """One persistent decode step on all emulated ranks.  dsts: list over tensors of per-rank
         HeapTensor lists of shape [2, cap * world, cols]; step_metas: per-rank int32[8]."""
         args = []
         for r in range(self.world):
             a = _ext.McbDenseStepArgs()
             for i in range(len(srcs)):
-                rb = srcs[i][r].shape[1] * srcs[i][r].element_size()
-                a.src[i], a.dst_off[i], a.row_bytes[i] = srcs[i][r].data_ptr(), dsts[i][r].offset, rb
+                if fp8_hidden and i in (0, 3):      # quantised rows / their scales (no source for the scales)
+                    rb = fp8_hidden if i == 0 else fp8_hidden // 128 * 4
+                else:
+                    rb = srcs[i][r].shape[1] * srcs[i][r].element_size()
+                a.src[i] = srcs[i][r].data_ptr() if srcs[i] is not None else 0
+                a.dst_off[i], a.row_bytes[i] = dsts[i][r].offset, rb
                 a.dst_par_stride[i] = dsts[i][r].tensor.shape[1] * rb
-            a.num_tensors, a.cap, a.num_layers = len(srcs), cap, num_layers
+            a.num_tensors, a.cap, a.num_layers, a.fp8_hidden = len(srcs), cap, num_layers, fp8_hidden
             a.rsv_dtype = 1 if outs[r].dtype == torch.float32 else 0
             a.out, a.rsv_off = outs[r].data_ptr(), rsv[r].offset
             a.rsv_row_bytes = outs[r].shape[1] * outs[r].element_size()
@@ -172,6 +180,60 @@ class EmuWorld:
         _ext.check(_ext.require().mcb_emu_dense_step(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
                                                      C.byref(args[0]), self.world, grid, threads, self._stream()),
                    "emu dense step")
+        torch.cuda.synchronize()
+
+    def moe_layer(self, ranks: list[dict], grid: int, topk: int, cap: int, ll_rows: int = 0, timeout_s: float = 2.0):
+        """One whole MoE layer (``moe_layer_kernel``: dispatch, routing, experts, combine) on all
+        emulated ranks in one cooperative launch; ``grid`` CTAs per rank, so grid * world must not
+        exceed the number of SMs.  Each entry of ``ranks`` holds that rank's tensors: ``weights``
+        (ExpertWeights), ``route`` (RouteBuffers), ``src`` = (hidden, routing, probs) local inputs,
+        ``dst`` = (hidden, routing, probs) gathered HeapTensors, ``partial`` (HeapTensor), ``n_local``,
+        ``step_meta``, ``act``, ``y``, ``out``, ``expert_begin`` and optionally ``ll_stage``."""
+        stride = _ext.layer_args_size()
+        blob = bytearray(stride * self.world)
+        first = None
+        for r, d in enumerate(ranks):
+            p = _ext.McbLayerArgs()
+            w, route = d["weights"], d["route"]
+            C.memmove(C.addressof(p.w1), w.map_w1[1], 128)
+            C.memmove(C.addressof(p.w2), w.map_down[1], 128)
+            C.memmove(C.addressof(p.ctx), C.addressof(self.ctxs[r]), C.sizeof(_ext.McbCtx))
+            a = p.agv
+            for i, (src, dst) in enumerate(zip(d["src"], d["dst"])):
+                a.src[i], a.dst_off[i] = src.data_ptr(), dst.offset
+                a.row_bytes[i] = src.shape[1] * src.element_size()
+            a.num_tensors, a.cap, a.site = 3, cap, _ext.SITE_AGV
+            a.n_local, a.step_meta = d["n_local"].data_ptr(), d["step_meta"].data_ptr()
+            if ll_rows > 0:
+                a.ll_off, a.ll_rows = d["ll_stage"].offset, ll_rows
+            ro = p.route
+            ro.topk_idx, ro.topk_w = d["dst"][1].tensor.data_ptr(), d["dst"][2].tensor.data_ptr()
+            ro.num_tokens = d["step_meta"].data_ptr()
+            ro.topk, ro.expert_begin, ro.num_local_experts, ro.max_tokens = topk, d["expert_begin"], route.E, route.max_tokens
+            for f in ("expert_count", "expert_cursor", "expert_offset", "pair_token", "pair_prob", "pair_pos",
+                      "tile_expert", "tile_row0", "tile_rows", "num_m_tiles", "sync", "max_rows", "ffn_done"):
+                setattr(ro, f, getattr(route, f).data_ptr())
+            ro.max_pairs, ro.max_tiles = route.max_pairs, route.max_tiles
+            ro.status, ro.timeout_ns = self.status[r].data_ptr(), int(timeout_s * 1e9)
+            ff = p.ffn
+            ff.x, ff.x_row_bytes = d["dst"][0].tensor.data_ptr(), w.hidden * 2
+            ff.pair_token, ff.pair_prob = route.pair_token.data_ptr(), route.pair_prob.data_ptr()
+            ff.expert_offset, ff.max_rows = route.expert_offset.data_ptr(), route.max_rows.data_ptr()
+            ff.act, ff.y, ff.ffn_done = d["act"].data_ptr(), d["y"].data_ptr(), route.ffn_done.data_ptr()
+            ff.num_local_experts, ff.hidden, ff.intermediate = w.num_local_experts, w.hidden, w.intermediate
+            ff.status, ff.timeout_ns = self.status[r].data_ptr(), int(timeout_s * 1e9)
+            cm = p.cmb
+            cm.y, cm.pair_pos, cm.partial_off, cm.out = d["y"].data_ptr(), route.pair_pos.data_ptr(), d["partial"].offset, d["out"].data_ptr()
+            cm.n_local, cm.step_meta = d["n_local"].data_ptr(), d["step_meta"].data_ptr()
+            cm.hidden, cm.topk, cm.cap, cm.site = w.hidden, topk, cap, _ext.SITE_FUSED_FC2
+            blob[r * stride:r * stride + C.sizeof(p)] = bytes(p)
+            if first is None:
+                first = p
+        dev_args = torch.frombuffer(blob, dtype=torch.uint8).to(self.device)
+        if dev_args.data_ptr() % 64:
+            raise RuntimeError("device allocation is not 64-byte aligned")
+        _ext.check(_ext.require().mcb_emu_moe_layer(C.c_void_p(dev_args.data_ptr()), C.byref(first), self.world, grid,
+                                                    self._stream()), "emu moe layer")
         torch.cuda.synchronize()
 
     def barrier_test(self, grid=2, rounds=1):
@@ -228,6 +290,43 @@ class EmuWorld:
         self._level(_ext.SITE_A2A_COMBINE, grid)
         _ext.check(_ext.require().mcb_emu_a2a_combine(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
                                                       self.world, grid, threads, self._stream()), "emu a2a combine")
+        torch.cuda.synchronize()
+
+    def a2a_step_buffers(self, cap, hidden, topk, fp8):
+        from ..ops.a2a import a2a_meta_row_bytes
+        w = self.world
+        b = {"cap": cap, "hidden": hidden, "topk": topk, "fp8": fp8, "meta_row_bytes": a2a_meta_row_bytes(topk)}
+        if fp8:
+            b["recv_x"] = self.alloc([2, w, cap, hidden], torch.uint8)
+            b["recv_scale"] = self.alloc([2, w, cap, hidden // 128], torch.float32)
+            b["y"] = self.alloc([2, w, cap, hidden], torch.bfloat16)
+        else:
+            b["recv_x"] = self.alloc([2, w, cap, hidden], torch.bfloat16)
+            b["recv_scale"] = None
+            b["y"] = b["recv_x"]
+        b["recv_meta"] = self.alloc([2, w, cap, b["meta_row_bytes"]], torch.uint8)
+        return b
+
+    def a2a_step(self, b, xs, idxs, ws, outs, n_locals, step_metas, num_experts, num_layers, grid=4, threads=256):
+        """One persistent all-to-all decode step on all emulated ranks."""
+        args = []
+        for r in range(self.world):
+            a = _ext.McbA2AStepArgs()
+            a.x, a.topk_idx, a.topk_w, a.out = xs[r].data_ptr(), idxs[r].data_ptr(), ws[r].data_ptr(), outs[r].data_ptr()
+            a.n_local = n_locals[r].data_ptr()
+            a.recv_x_off, a.x_par_stride = b["recv_x"][r].offset, b["recv_x"][r].nbytes // 2
+            if b["recv_scale"]:
+                a.recv_scale_off, a.scale_par_stride = b["recv_scale"][r].offset, b["recv_scale"][r].nbytes // 2
+            a.recv_meta_off, a.meta_par_stride = b["recv_meta"][r].offset, b["recv_meta"][r].nbytes // 2
+            a.y_off, a.y_par_stride = b["y"][r].offset, b["y"][r].nbytes // 2
+            a.meta_row_bytes, a.hidden, a.topk, a.num_experts = b["meta_row_bytes"], b["hidden"], b["topk"], num_experts
+            a.cap, a.fp8, a.num_layers = b["cap"], int(b["fp8"]), num_layers
+            a.step_meta, a.counts_off, a.state = step_metas[r].data_ptr(), self.a2a_counts_off, self.a2a_state[r].data_ptr()
+            args.append(a)
+        d = self.upload(args)
+        _ext.check(_ext.require().mcb_emu_a2a_step(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),
+                                                   C.byref(self.ctxs[0]), C.byref(args[0]), self.world, grid, threads,
+                                                   self._stream()), "emu a2a step")
         torch.cuda.synchronize()
 
     def rs_add_norm_ag(self, buf, residuals, weight, eps, grid=4):

@@ -11,11 +11,12 @@ expert computation the transport exists for.  Per layer and rank:
     FC2        y = prob * (act Wd^T)                              csrc/gemm.cu    grouped_gemm_kernel<FC2>
     combine    out[t] = sum_ranks sum_local-pairs y               csrc/route.cu   combine_kernel
 
-By default the layer is TWO kernels.  Dispatch, routing and FC1 are one
-(``dispatch_route_fc1_kernel``: multicast push + cross-GPU barrier, grid barrier, routing, grid
-barrier, GEMM; ``fuse_dispatch=False`` launches the three separately), and FC2 and the combine are one (``fc2_combine_kernel`` in csrc/gemm.cu: the GEMM
-CTAs finish their tiles, meet in a grid-wide barrier and run the combine, multimem.ld_reduce
-included); ``fuse_combine=False`` launches them separately.
+By default the whole layer is ONE cooperative kernel (``moe_layer_kernel`` in csrc/ffn.cu: dispatch,
+grid barrier, routing, grid barrier, the grouped FFN with the weights as the M = 128 operand and both
+projections in one persistent weight stream, grid barrier, combine), and a decode step is issued by
+one native call (count exchange + one launch per layer).  ``layer_kernel=False`` selects the older
+form with the tokens as the M operand: two kernels per layer (``dispatch_route_fc1_kernel`` and
+``fc2_combine_kernel`` in csrc/gemm.cu), or five with ``fuse_dispatch=False`` / ``fuse_combine=False``.
 
 Weights: 512 experts x 3 x 1024^2 bf16 is 3.2 GB per layer; every layer gets its own set while
 they fit in ``weight_budget_gb`` per GPU, after which sets are reused round-robin (each set is
@@ -29,8 +30,8 @@ import torch.distributed as dist
 from ..config import Config
 from ..ops import _ext, oracle
 from ..ops.dense import AllGatherVPlan, MetadataPlan, DEFAULT_GRID, DEFAULT_THREADS, agv_ll_stage_bytes
-from ..ops.experts import (DispatchRouteFc1Plan, ExpertCombinePlan, ExpertWeights, Fc2CombinePlan, GroupedGemmPlan, RouteBuffers, RoutePlan,
-                           NUM_SMS)
+from ..ops.experts import (DispatchRouteFc1Plan, ExpertCombinePlan, ExpertFfnPlan, ExpertWeights, Fc2CombinePlan,
+                           GroupedGemmPlan, MoeLayerPlan, RouteBuffers, RoutePlan, NUM_SMS)
 from .base import Dispatcher
 from .dense import resolve_ll_rows
 from .symm_heap import SymmetricHeap, required_bytes
@@ -42,7 +43,8 @@ class FusedExpertDispatcher(Dispatcher):
     def __init__(self, cfg: Config, group, heap: SymmetricHeap | None = None, num_sms: int = DEFAULT_GRID,
                  threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto", ll_rows: int = -1,
                  num_layers: int = 88, weight_budget_gb: float = 64.0, weight_seed: int = 7,
-                 fuse_combine: bool = True, fuse_dispatch: bool = True, coop_pdl: bool = False, device=None):
+                 fuse_combine: bool = True, fuse_dispatch: bool = True, coop_pdl: bool = False,
+                 layer_kernel: bool = True, device=None):
         super().__init__(cfg, group, device)
         self.heap, self._own_heap = heap, heap is None
         self.num_sms, self.threads, self.pdl, self.transport = int(num_sms), int(threads), bool(pdl), transport
@@ -51,7 +53,9 @@ class FusedExpertDispatcher(Dispatcher):
         self.fuse_combine = bool(fuse_combine)
         self.coop_pdl = bool(coop_pdl)   # cooperative + programmatic dependent launch on the fused kernel
         self.fuse_dispatch = bool(fuse_dispatch)
-        self.kernel_launches_per_step = lambda nl: 1 + (5 - int(self.fuse_combine) - 2 * int(self.fuse_dispatch)) * nl
+        self.layer_kernel = bool(layer_kernel)
+        self.kernel_launches_per_step = lambda nl: 1 + (
+            1 if self.layer_kernel else 5 - int(self.fuse_combine) - 2 * int(self.fuse_dispatch)) * nl
 
     @staticmethod
     def heap_specs(cfg: Config, ll_rows: int = -1):
@@ -86,7 +90,8 @@ class FusedExpertDispatcher(Dispatcher):
         self.y = torch.zeros(max(self.route.max_pairs, 1), H, dtype=torch.bfloat16, device=dev)
         per_layer = E * 3 * H * I * 2
         sets = max(1, min(self.num_layers, int(self.weight_budget_gb * 2**30 // per_layer)))
-        self.weights = [ExpertWeights(E, H, I, dev, seed=self.weight_seed * 100003 + s * 1009 + cfg.rank)
+        self.weights = [ExpertWeights(E, H, I, dev, seed=self.weight_seed * 100003 + s * 1009 + cfg.rank,
+                                      layout="interleaved" if self.layer_kernel else "split")
                         for s in range(sets)]
         st = h.status.view(torch.int32)
         self.meta_plan = MetadataPlan(h, self.n_local, self.step_metadata, cap)
@@ -96,14 +101,18 @@ class FusedExpertDispatcher(Dispatcher):
                                        ll_stage=self.ll_agv, ll_rows=self.ll_rows)
         self.route_plan = RoutePlan(self.route, self.agv_r.tensor, self.agv_p.tensor, self.step_metadata[0:1],
                                     expert_begin=cfg.rank * E, status=st)
-        self.fc1 = [GroupedGemmPlan(_ext.GEMM_FC1, w.map_gate_up, self.route, self.agv_h.tensor, self.act, 2 * I, H, st)
-                    for w in self.weights]
-        self.fc2 = [GroupedGemmPlan(_ext.GEMM_FC2, w.map_down, self.route, self.act, self.y, H, I, st)
-                    for w in self.weights]
         self.combine_plan = ExpertCombinePlan(h, self.y, self.route, self.partial, self.out_buf, self.n_local,
                                               self.step_metadata, cap, grid=NUM_SMS)
-        self.fc2_combine = [Fc2CombinePlan(h, f, self.combine_plan) for f in self.fc2]
-        self.dispatch_fc1 = [DispatchRouteFc1Plan(h, self.agv_plan, self.route_plan, f) for f in self.fc1]
+        if self.layer_kernel:
+            self.ffn = [ExpertFfnPlan(w, self.route, self.agv_h.tensor, self.act, self.y, st) for w in self.weights]
+            self.layer_plan = MoeLayerPlan(h, self.agv_plan, self.route_plan, self.ffn, self.combine_plan, self.meta_plan)
+        else:
+            self.fc1 = [GroupedGemmPlan(_ext.GEMM_FC1, w.map_gate_up, self.route, self.agv_h.tensor, self.act, 2 * I, H, st)
+                        for w in self.weights]
+            self.fc2 = [GroupedGemmPlan(_ext.GEMM_FC2, w.map_down, self.route, self.act, self.y, H, I, st)
+                        for w in self.weights]
+            self.fc2_combine = [Fc2CombinePlan(h, f, self.combine_plan) for f in self.fc2]
+            self.dispatch_fc1 = [DispatchRouteFc1Plan(h, self.agv_plan, self.route_plan, f) for f in self.fc1]
         torch.cuda.synchronize()
         dist.barrier(self.group)
         self._built = True
@@ -132,14 +141,20 @@ class FusedExpertDispatcher(Dispatcher):
     def experts(self, layer: int = 0):
         s = layer % len(self.weights)
         self.route_plan.launch(self.pdl)
-        self.fc1[s].launch(self.pdl)
-        self.fc2[s].launch(self.pdl)
+        if self.layer_kernel:
+            self.ffn[s].launch(self.pdl)
+        else:
+            self.fc1[s].launch(self.pdl)
+            self.fc2[s].launch(self.pdl)
 
     def combine(self):
         self.combine_plan.launch(self.pdl)
 
     def layer(self, layer: int = 0):
         s = layer % len(self.weights)
+        if self.layer_kernel:
+            self.layer_plan.launch(s, self.pdl and self.coop_pdl)
+            return
         if self.fuse_dispatch:
             self.dispatch_fc1[s].launch(self.pdl and self.coop_pdl)
         else:
@@ -156,6 +171,9 @@ class FusedExpertDispatcher(Dispatcher):
         self.layer(0)
 
     def decode_step(self, num_layers: int):
+        if self.layer_kernel:       # one native call: count exchange + one launch per layer
+            self.layer_plan.decode_step(num_layers, self.pdl and self.coop_pdl)
+            return
         self.metadata()
         for l in range(num_layers):
             self.layer(l)
@@ -174,14 +192,15 @@ class FusedExpertDispatcher(Dispatcher):
         s = layer % len(self.weights)
         wgu, wd = [], []
         for r in range(cfg.ep_size):
-            w = self.weights[s] if r == cfg.rank else ExpertWeights.__new__(ExpertWeights)
-            if r != cfg.rank:
+            if r == cfg.rank:
+                gu, dn = self.weights[s].w_gate_up, self.weights[s].w_down
+            else:   # the same generator calls as ExpertWeights.__init__, with that rank's seed
                 g = torch.Generator(device=self.device).manual_seed(self.weight_seed * 100003 + s * 1009 + r)
                 E, H, I = cfg.num_local_experts, cfg.hidden, cfg.intermediate
-                w.w_gate_up = (torch.randn(E, 2 * I, H, device=self.device, generator=g) * 0.02).to(torch.bfloat16)
-                w.w_down = (torch.randn(E, H, I, device=self.device, generator=g) * 0.02).to(torch.bfloat16)
-            wgu.append(w.w_gate_up.cpu())
-            wd.append(w.w_down.cpu())
+                gu = (torch.randn(E, 2 * I, H, device=self.device, generator=g) * 0.02).to(torch.bfloat16)
+                dn = (torch.randn(E, H, I, device=self.device, generator=g) * 0.02).to(torch.bfloat16)
+            wgu.append(gu.cpu())
+            wd.append(dn.cpu())
         return oracle.moe_layer(hidden.cpu(), topk_idx.cpu(), topk_w.cpu(), torch.cat(wgu), torch.cat(wd))
 
     def validate(self):

@@ -30,8 +30,9 @@ from ..ops import _ext
 ALIGN = 256
 FLAGS_BYTES = _ext.NUM_SITES * _ext.MAX_BLOCKS * 4
 COUNTS_BYTES = 2 * _ext.MAX_RANKS * 4          # counts of the metadata kernel (two parities)
-STEP_COUNTS_BYTES = 2 * _ext.MAX_RANKS * 4     # counts of the persistent step kernel (two parities)
-RESERVED_BYTES = ((FLAGS_BYTES + COUNTS_BYTES + STEP_COUNTS_BYTES + ALIGN - 1) // ALIGN) * ALIGN
+STEP_COUNTS_BYTES = 2 * _ext.MAX_RANKS * 4     # counts of the persistent dense step kernel (two parities)
+A2A_COUNTS_BYTES = 2 * _ext.MAX_RANKS * 4      # counts of the persistent all-to-all step kernel
+RESERVED_BYTES = ((FLAGS_BYTES + COUNTS_BYTES + STEP_COUNTS_BYTES + A2A_COUNTS_BYTES + ALIGN - 1) // ALIGN) * ALIGN
 
 
 class DeviceStatusError(RuntimeError):
@@ -189,6 +190,10 @@ class SymmetricHeap:
     @property
     def step_counts_off(self) -> int:
         return FLAGS_BYTES + COUNTS_BYTES
+
+    @property
+    def a2a_counts_off(self) -> int:
+        return FLAGS_BYTES + COUNTS_BYTES + STEP_COUNTS_BYTES
 
     def peer_view(self, peer: int, ht: HeapTensor) -> torch.Tensor:
         """This rank's mapping of ``peer``'s copy of a heap tensor (debug / validation only)."""

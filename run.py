@@ -18,6 +18,11 @@ implementations behind ``--impl`` are this repository's own:
   fused                 dense transport fused with real SwiGLU experts (tcgen05 grouped GEMMs)
   gloo                  the dense algorithm on CPU ranks (no GPU needed)
   both = a2a + dense,  all = a2a + dense + nccl
+
+``--expert swiglu`` replaces the identity expert by a real SwiGLU FFN per expert: ``--impl dense`` (or
+``fused``) then runs the fused expert path, and ``--impl nccl`` an EXTENDED baseline that the reference
+does not have (NCCL all-gather x3 + library grouped GEMMs + fp32 NCCL reduce-scatter, reported as
+``nccl-swiglu``), so that the fused path has something to be compared with.
 """
 from __future__ import annotations
 
@@ -65,7 +70,14 @@ def parse_args(argv=None):
     p.add_argument("--routing", choices=["uniform", "zipf"], default="uniform")
     p.add_argument("--counts", choices=["balanced", "multinomial"], default="balanced")
     p.add_argument("--dispatch-dtype", choices=["bf16", "fp8"], default="bf16")
-    p.add_argument("--expert", choices=["identity", "swiglu"], default="identity")
+    p.add_argument("--expert", choices=["identity", "swiglu"], default="identity",
+                   help="swiglu: real experts (dense/fused -> the fused expert path, nccl -> NCCL + library GEMMs)")
+    p.add_argument("--no-persistent", action="store_true",
+                   help="dense: one kernel per operation (1 + 2 x layers launches) instead of one per decode step")
+    p.add_argument("--groups", type=int, default=1,
+                   help="dense: pipeline groups of the persistent step kernel (1 = none)")
+    p.add_argument("--no-layer-kernel", action="store_true",
+                   help="fused: the two-kernel form with tokens as the M operand instead of one kernel per layer")
     p.add_argument("--dense-num-sms", type=int, default=148, help="CTA cap of the dense kernels")
     p.add_argument("--transport", choices=["auto", "multimem", "p2p"], default="auto")
     p.add_argument("--ll-rows", type=int, default=-1,
@@ -84,12 +96,18 @@ def parse_args(argv=None):
     return p.parse_args(argv)
 
 
-def resolve_impls(impl: str, on_gpu: bool) -> list[str]:
+def resolve_impls(impl: str, on_gpu: bool, expert: str = "identity") -> list[str]:
     if not on_gpu:
         return ["gloo"]
     table = {"deepep": ["a2a"], "a2a": ["a2a"], "nvls": ["dense"], "dense": ["dense"], "nccl": ["nccl"],
              "both": ["a2a", "dense"], "all": ["a2a", "dense", "nccl"], "fused": ["fused"], "gloo": ["gloo"]}
-    return table[impl]
+    names = table[impl]
+    if expert == "swiglu":      # real experts: the fused path, and the extended NCCL baseline
+        swap = {"dense": "fused", "fused": "fused", "nccl": "nccl-swiglu"}
+        if any(n not in swap for n in names):
+            raise SystemExit("--expert swiglu is available for --impl dense, fused and nccl")
+        names = [swap[n] for n in names]
+    return names
 
 
 def make_config(args, world, rank, local_rank, batch_sizes) -> tuple[Config, int]:
@@ -112,7 +130,7 @@ def build_dispatchers(names, cfg, group, args, device, sms_list):
         from moe_comms_benchmarking_b200.parallel.dense import DenseDispatcher
         specs = []
         if "dense" in names:
-            specs += DenseDispatcher.heap_specs(cfg, ll_rows=args.ll_rows)
+            specs += DenseDispatcher.heap_specs(cfg, ll_rows=args.ll_rows, fp8=fp8)
         if "a2a" in names:
             specs += A2ADispatcher.heap_specs(cfg, fp8)
         if "fused" in names:
@@ -124,16 +142,22 @@ def build_dispatchers(names, cfg, group, args, device, sms_list):
             out.append(A2ADispatcher(cfg, group, heap, num_sms=sms_list[0], pdl=not args.no_pdl, fp8_dispatch=fp8))
         elif n == "dense":
             out.append(DenseDispatcher(cfg, group, heap, num_sms=args.dense_num_sms, pdl=not args.no_pdl,
-                                       ll_rows=args.ll_rows))
+                                       ll_rows=args.ll_rows, persistent=not args.no_persistent, groups=args.groups,
+                                       fp8_dispatch=fp8))
         elif n == "fused":
             out.append(FusedExpertDispatcher(cfg, group, heap, pdl=not args.no_pdl, ll_rows=args.ll_rows,
                                              num_layers=1 if args.validate else (args.num_layers or 88),
                                              weight_budget_gb=args.weight_budget_gb,
                                              fuse_combine=not args.no_fuse_combine,
-                                             fuse_dispatch=not args.no_fuse_dispatch, coop_pdl=args.coop_pdl))
+                                             fuse_dispatch=not args.no_fuse_dispatch, coop_pdl=args.coop_pdl,
+                                             layer_kernel=not args.no_layer_kernel))
         elif n == "nccl":
             from moe_comms_benchmarking_b200.parallel.nccl import NCCLDispatcher
             out.append(NCCLDispatcher(cfg, group))
+        elif n == "nccl-swiglu":
+            from moe_comms_benchmarking_b200.parallel.nccl import NCCLSwiGLUDispatcher
+            out.append(NCCLSwiGLUDispatcher(cfg, group, num_layers=1 if args.validate else (args.num_layers or 88),
+                                            weight_budget_gb=args.weight_budget_gb))
         elif n == "gloo":
             from moe_comms_benchmarking_b200.parallel.gloo import GlooDenseDispatcher
             out.append(GlooDenseDispatcher(cfg, group))
@@ -193,7 +217,7 @@ def main(argv=None) -> int:
     dev_sms = torch.cuda.get_device_properties(local_rank).multi_processor_count if on_gpu else 0
     even = lambda s: max(2, min(int(s), dev_sms or int(s)) - (min(int(s), dev_sms or int(s)) % 2))  # noqa: E731
     sms_sweep = sorted({even(s) for s in args.deepep_num_sms.split(",")})
-    names = resolve_impls(args.impl, on_gpu)
+    names = resolve_impls(args.impl, on_gpu, args.expert)
     if rank == 0:
         say("# MoE dispatch/combine decode benchmark")
         say(f"# EP={world} experts={cfg.num_experts} topk={cfg.topk} hidden={cfg.hidden} "

@@ -24,6 +24,11 @@ def test_cli_defaults_match_reference_driver():
                         ("all", ["a2a", "dense", "nccl"])):
         assert run.resolve_impls(alias, True) == want
     assert run.resolve_impls("all", False) == ["gloo"]
+    # real experts: the fused path and the extended NCCL baseline
+    assert run.resolve_impls("dense", True, "swiglu") == ["fused"]
+    assert run.resolve_impls("nccl", True, "swiglu") == ["nccl-swiglu"]
+    with pytest.raises(SystemExit):
+        run.resolve_impls("a2a", True, "swiglu")
     with pytest.raises(SystemExit):
         run.parse_args(["--impl", "bogus"])
     a = run.parse_args(["--model", "deepseek-v3", "--num-layers", "3", "--dispatch-dtype", "fp8"])

@@ -101,6 +101,53 @@ def test_step_kernel_fp32_combine(lib):
     rig.w.check_status()
 
 
+@pytest.mark.parametrize("grid,threads", [(2, 128), (8, 256)])
+def test_step_kernel_fp8_dispatch(lib, grid, threads):
+    """1 x 128 block-scaled e4m3 dispatch inside the step kernel, in barrier mode and in packet mode:
+    scales == amax / 448, values within e4m3 rounding of the inputs (against the CPU oracle's
+    quantiser), routing / probs bit-exact, combine unaffected."""
+    W, cap, H, K, LL = 4, 16, 512, 6, 8
+    w = EmuWorld(W, 16 << 20, DEV)
+    dst_q = w.alloc([2, cap * W, H], torch.uint8)
+    dst_r = w.alloc([2, cap * W, K], torch.int64)
+    dst_p = w.alloc([2, cap * W, K], torch.float32)
+    dst_s = w.alloc([2, cap * W, H // 128], torch.float32)
+    rsv = w.alloc([cap * W, H], torch.bfloat16)
+    st_a = w.alloc([agv_ll_stage_bytes(LL, [H, K * 8, K * 4, H // 128 * 4])], torch.uint8)
+    st_r = w.alloc([rsv_ll_stage_bytes(W, LL, cap, H * 2)], torch.uint8)
+    metas = [torch.zeros(8, dtype=torch.int32, device=DEV) for _ in range(W)]
+    outs = [torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV) for _ in range(W)]
+    g = torch.Generator(device=DEV).manual_seed(5)
+    for counts, layers, mode in (([5, 0, 16, 3], 2, 0), ([1, 2, 3, 2], 3, 1), ([16, 16, 16, 16], 1, 0), ([0, 1, 0, 0], 2, 1)):
+        src_h = [(torch.randn(cap, H, device=DEV, generator=g) * (1 + r)).to(torch.bfloat16) for r in range(W)]
+        src_h[1][0, :128] = 0                      # an all-zero block
+        src_r = [torch.randint(0, 512, (cap, K), device=DEV, generator=g) for _ in range(W)]
+        src_p = [torch.rand(cap, K, device=DEV, generator=g) for _ in range(W)]
+        for r in range(W):
+            rsv[r].tensor.copy_(torch.randn(cap * W, H, device=DEV, generator=g).to(torch.bfloat16))
+        w.dense_step([dst_q, dst_r, dst_p, dst_s], [src_h, src_r, src_p, None], outs, rsv, _scalars(counts), metas, cap,
+                     layers, grid=grid, threads=threads, agv_ll_stage=st_a, rsv_ll_stage=st_r, ll_rows=LL, fp8_hidden=H)
+        valid = sum(counts)
+        full_h = oracle.all_gather_v([src_h[r][:counts[r]] for r in range(W)]).float().cpu()
+        full_r = oracle.all_gather_v([src_r[r][:counts[r]] for r in range(W)])
+        full_p = oracle.all_gather_v([src_p[r][:counts[r]] for r in range(W)])
+        q_ref, s_ref = oracle.quant_e4m3_1x128(full_h)
+        want = oracle.reduce_scatter_v([rsv[r].tensor[:valid].cpu() for r in range(W)], counts)
+        for r in range(W):
+            m = metas[r].tolist()
+            assert m[6] == mode
+            par = m[5]
+            sc = dst_s[r].tensor[par, :valid].cpu()
+            q = dst_q[r].tensor[par, :valid].cpu().view(torch.float8_e4m3fn)
+            assert torch.allclose(sc, s_ref, rtol=1e-6, atol=0)
+            back = oracle.dequant_e4m3_1x128(q, sc)
+            assert ((back - full_h).abs() <= 0.0625 * full_h.abs() + 2e-3 * sc.repeat_interleave(128, dim=1)).all()
+            assert (q.float() == q_ref.float()).float().mean() > 0.999
+            assert torch.equal(dst_r[r].tensor[par, :valid], full_r) and torch.equal(dst_p[r].tensor[par, :valid], full_p)
+            assert torch.allclose(outs[r][:counts[r]].float().cpu(), want[r], rtol=2e-2, atol=2e-2)
+    w.check_status()
+
+
 def test_step_kernel_bounded_wait_with_a_phantom_rank(lib):
     """A world that counts a rank which never runs: the count exchange cannot complete, the
     bounded wait runs out, the status words say so and the GPU context stays usable."""

@@ -202,6 +202,59 @@ def test_launch_numbers_do_not_depend_on_the_grid(lib):
     w.check_status()
 
 
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("grid,threads", [(1, 64), (6, 256)])
+def test_a2a_step_kernel(lib, fp8, grid, threads):
+    """The persistent all-to-all step (count exchange + every layer in one launch): token-indexed
+    slots, packed metadata rows with the layer's stamp, one barrier per layer; steps of 1-3 layers with
+    idle ranks; received rows / routing / stamps and the combined m * x against the oracle."""
+    W, E, K, H, cap = 4, 32, 6, 512, 12
+    w = EmuWorld(W, 16 << 20, DEV)
+    b = w.a2a_step_buffers(cap, H, K, fp8)
+    g = torch.Generator(device=DEV).manual_seed(29)
+    metas = [torch.zeros(8, dtype=torch.int32, device=DEV) for _ in range(W)]
+    outs = [torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV) for _ in range(W)]
+    epr = E // W
+    for counts, layers in (([5, 0, 12, 3], 3), ([1, 0, 0, 0], 2), ([0, 0, 0, 0], 1), ([12, 12, 12, 12], 2), ([2, 7, 1, 4], 1)):
+        xs = [torch.randn(cap, H, device=DEV, generator=g).to(torch.bfloat16) for _ in range(W)]
+        idxs = [torch.stack([torch.randperm(E, device=DEV, generator=g)[:K] for _ in range(cap)]) for _ in range(W)]
+        ws = [torch.rand(cap, K, device=DEV, generator=g) for _ in range(W)]
+        if fp8:
+            xs[0][0, :128] = 0
+        w.a2a_step(b, xs, idxs, ws, outs, _scalars(counts), metas, E, layers, grid=grid, threads=threads)
+        par, stamp = int(metas[0][5]), int(metas[0][7])
+        assert metas[0][:3].tolist() == oracle.metadata(counts)[0]
+        for d in range(W):
+            for s in range(W):
+                c = counts[s]
+                if not c:
+                    continue
+                words = b["recv_meta"][d].tensor[par, s, :c].view(torch.int32).view(c, -1)
+                here = ((idxs[s][:c] // epr) == d).any(dim=1)
+                assert torch.equal(words[:, 0] == stamp, here)
+                sel = here.nonzero().flatten()
+                if not sel.numel():
+                    continue
+                assert torch.equal(words[sel, 1].long(), sel)
+                assert torch.equal(words[sel][:, 2:2 + 2 * K:2].long(), idxs[s][sel])
+                assert torch.equal(words[sel][:, 3:3 + 2 * K:2].contiguous().view(torch.float32), ws[s][sel])
+                if fp8:
+                    q = b["recv_x"][d].tensor[par, s][sel].cpu().view(torch.float8_e4m3fn)
+                    sc = b["recv_scale"][d].tensor[par, s][sel].cpu()
+                    want = xs[s][sel].float().cpu()
+                    _, s_ref = oracle.quant_e4m3_1x128(want)
+                    assert torch.allclose(sc, s_ref, rtol=1e-6, atol=0)
+                    back = oracle.dequant_e4m3_1x128(q, sc)
+                    assert ((back - want).abs() <= 0.0625 * want.abs() + 2e-3 * sc.repeat_interleave(128, dim=1)).all()
+                else:
+                    assert torch.equal(b["recv_x"][d].tensor[par, s][sel], xs[s][sel])
+        if not fp8:         # identity expert: the combine reads the received rows
+            for r in range(W):
+                ref = oracle.roundtrip_identity(xs[r][:counts[r]], idxs[r][:counts[r]].cpu(), E, W)
+                assert torch.allclose(outs[r][:counts[r]].float().cpu(), ref, rtol=2e-2, atol=2e-2)
+    w.check_status()
+
+
 def test_a2a_fp8_dispatch(lib):
     W, E, K, H, counts = 2, 16, 4, 512, [6, 3]
     w, b, xs, idxs, ws, n_locals, cap = _a2a_case(W, E, K, H, counts, True, 13)
