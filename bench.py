@@ -50,6 +50,10 @@ def parse_args(argv=None):
     p.add_argument("--groups", type=int, default=-1, help="pipeline groups of the persistent dense step kernel "
                                                           "(-1 = the dispatcher's default)")
     p.add_argument("--no-persistent", action="store_true", help="one kernel per operation instead of one per step")
+    p.add_argument("--fused-sweep", default="64,512,4096",
+                   help="global batches of the real-expert (fused SwiGLU) path reported under 'fused_ms_by_global_batch' "
+                        "(empty = skip)")
+    p.add_argument("--fused-weight-gb", type=float, default=40.0, help="GPU memory for the expert weights of that path")
     return p.parse_args(argv)
 
 
@@ -122,8 +126,30 @@ def run_native(args):
     # end to end: pinned host inputs in, combined output out, every step
     hp, ip, wp = pinned_inputs(h, i, w)
     e2e_ms = timed_steps(lambda: eng.step_host(hp, ip, wp), args.steps, args.warmup, group, flush)
-    clocks = sampler.stop() if sampler is not None else None
     eng.check_health()
+    # The same step with REAL experts (SwiGLU FFN per expert, one fused kernel per layer): reported next to
+    # the headline, never part of it.  A failure here must not cost the headline line.
+    fused_ms, fused_detail = {}, {}
+    fused_sweep = [int(b) for b in args.fused_sweep.split(",") if b.strip()]
+    if fused_sweep:
+        try:
+            fcfg = Config(ep_size=world, rank=rank, local_rank=local_rank, per_rank_cap=-(-max(fused_sweep) // world))
+            feng = MoEDecodeEngine(fcfg, group, impl="fused", num_layers=NUM_LAYERS, pdl=not args.no_pdl,
+                                   weight_budget_gb=args.fused_weight_gb).build()
+            feng.capture()
+            for b in fused_sweep:
+                fh, fi, fw = make_inputs(fcfg, b, dev)
+                feng.load_batch(fh, fi, fw)
+                fused_ms[str(b)] = round(timed_steps(feng.run, 5, 3, group, flush), 4)
+                feng.check_health()
+            per_layer_mb = fcfg.num_local_experts * 3 * fcfg.hidden * fcfg.intermediate * 2 / 1e6
+            fused_detail = {"kernels_per_step": feng.dispatcher.kernel_launches_per_step(NUM_LAYERS),
+                            "weight_sets": len(feng.dispatcher.weights), "weights_mb_per_layer_and_rank": round(per_layer_mb, 1),
+                            "expert": "SwiGLU FFN, hidden 1024 -> intermediate 1024 -> 1024, bf16, N(0, 0.02^2)"}
+            feng.destroy()
+        except Exception as e:     # keep the headline
+            fused_detail = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+    clocks = sampler.stop() if sampler is not None else None
     n = h.shape[0]
     h2d = n * (cfg.hidden * 2 + cfg.topk * 8 + cfg.topk * 4) + 4
     d2h = n * cfg.hidden * 2
@@ -150,6 +176,7 @@ def run_native(args):
             "e2e": {"value": round(e2e_ms, 4), "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
             "sweep_ms_by_global_batch": {k: round(v, 4) for k, v in sweep_ms.items()},
+            "fused_ms_by_global_batch": fused_ms, "fused_detail": fused_detail,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -46,7 +46,7 @@ def main(argv=None):
     heap = SymmetricHeap(None, cap * H * 2 + (1 << 20), dev)
     partial = heap.alloc("partial", [cap, H], torch.bfloat16)
     weights = ExpertWeights(E, H, I, dev, seed=1, layout="split")       # tokens-as-rows GEMM kernels
-    weights_il = ExpertWeights(E, H, I, dev, seed=1)                    # weights-as-M FFN kernel (interleaved gate/up)
+    weights_il = ExpertWeights(E, H, I, dev, seed=1)                    # weights-as-M FFN kernel (packed tiles)
     route = RouteBuffers(cap, K, E, dev)
     xs = torch.randn(cap, H, device=dev).to(torch.bfloat16)
     idxs = torch.zeros(cap, K, dtype=torch.int64, device=dev)

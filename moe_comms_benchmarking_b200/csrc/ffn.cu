@@ -26,12 +26,10 @@
 
 namespace mcb {
 
-__global__ void __launch_bounds__(kFfnThreads, 1)
-expert_ffn_kernel(const __grid_constant__ CUtensorMap w1, const __grid_constant__ CUtensorMap w2,
-                  const __grid_constant__ McbFfnArgs a) {
+__global__ void __launch_bounds__(kFfnThreads, 1) expert_ffn_kernel(const __grid_constant__ McbFfnArgs a) {
   pdl_wait();
   pdl_launch_dependents();
-  ffn_device(&w1, &w2, a);
+  ffn_device(a);
 }
 
 template <bool EMU>
@@ -39,6 +37,7 @@ __global__ void __launch_bounds__(kFfnThreads, 1)
 moe_layer_kernel(const __grid_constant__ McbLayerArgs p_, const McbLayerArgs* eargs) {
   const McbLayerArgs& p = EMU ? eargs[blockIdx.y] : p_;
   const McbCtx& c = p.ctx;
+  ffn_prefetch_weights(p.ffn);           // weights do not change between launches: no need to wait for the predecessor
   uint32_t ll_launch = 0;
   agv_device<MCB_SITE_FC1_FUSED>(c, p.agv, ll_launch);      // waits for the previous kernel first
   // The arrival counter is back at zero whenever a launch has ended (its last block resets it).
@@ -46,9 +45,9 @@ moe_layer_kernel(const __grid_constant__ McbLayerArgs p_, const McbLayerArgs* ea
   grid_sync(c, arrivals, gridDim.x);
   route_device(p.route);
   grid_sync(c, arrivals, 2u * gridDim.x);
-  ffn_device(&p.w1, &p.w2, p.ffn);
+  ffn_device(p.ffn);
   grid_sync(c, arrivals, 3u * gridDim.x);                   // every y row is written before any is summed
-  combine_body(c, p.cmb);
+  combine_body(c, p.cmb, ll_launch);      // partial sums alternate between two buffers, layer by layer
   launch_end(c, MCB_SITE_FC1_FUSED, ll_launch, arrivals);
 }
 
@@ -76,20 +75,18 @@ static bool configure_ffn_kernels() {
 
 static int check_ffn_args(const McbFfnArgs* a) {
   if (!a || !a->x || !a->pair_token || !a->expert_offset || !a->max_rows || !a->act || !a->y || !a->ffn_done) return 1;
+  if (!a->w1 || !a->w2 || (reinterpret_cast<uintptr_t>(a->w1) & 15) || (reinterpret_cast<uintptr_t>(a->w2) & 15)) return 1;
   if (a->num_local_experts < 1 || a->hidden < 128 || a->hidden % 128 || a->intermediate < 64 || a->intermediate % 64) return 1;
   if (a->x_row_bytes & 15) return 1;
   return 0;
 }
 
 // Gate/up + SwiGLU + down over the pair lists of a routing, as one persistent launch.
-int mcb_launch_expert_ffn(const void* w1_map, const void* w2_map, const McbFfnArgs* args, int grid, int pdl,
-                          cudaStream_t stream) {
-  if (grid < 1 || !w1_map || !w2_map || check_ffn_args(args)) return cudaErrorInvalidValue;
+int mcb_launch_expert_ffn(const McbFfnArgs* args, int grid, int pdl, cudaStream_t stream) {
+  if (grid < 1 || check_ffn_args(args)) return cudaErrorInvalidValue;
   if (!configure_ffn_kernels()) return cudaErrorUnknown;
   // A down block waits for gate/up blocks that other CTAs compute: all CTAs must be resident.
-  return launch_kernel(expert_ffn_kernel, dim3(grid), dim3(kFfnThreads), kFfnSmemBytes, stream, pdl, true,
-                       *reinterpret_cast<const CUtensorMap*>(w1_map), *reinterpret_cast<const CUtensorMap*>(w2_map),
-                       *args);
+  return launch_kernel(expert_ffn_kernel, dim3(grid), dim3(kFfnThreads), kFfnSmemBytes, stream, pdl, true, *args);
 }
 
 static int check_layer_args(const McbLayerArgs* p, int grid) {

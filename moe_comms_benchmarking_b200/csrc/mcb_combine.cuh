@@ -12,7 +12,7 @@
 
 namespace mcb {
 
-__device__ __forceinline__ void combine_body(const McbCtx& c, const McbCombineArgs& a) {
+__device__ __forceinline__ void combine_body(const McbCtx& c, const McbCombineArgs& a, uint32_t parity = 0u) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int T = a.step_meta[0], offset = a.step_meta[1];
   int n = *a.n_local;
@@ -28,7 +28,8 @@ __device__ __forceinline__ void combine_body(const McbCtx& c, const McbCombineAr
   const int packs = a.hidden / 8;
   const uint64_t row_bytes = (uint64_t)a.hidden * 2;
   const uint8_t* y = reinterpret_cast<const uint8_t*>(a.y);
-  uint8_t* partial = c.heap_local + a.partial_off;
+  const uint64_t partial_off = a.partial_off + (uint64_t)(parity & 1u) * a.partial_par_stride;
+  uint8_t* partial = c.heap_local + partial_off;
 
   for (int t = bid + warp * nact; t < T; t += nact * nwarps) {
     // Pair rows of this token on this rank: lanes read the token's routing slots in parallel,
@@ -79,7 +80,7 @@ __device__ __forceinline__ void combine_body(const McbCtx& c, const McbCombineAr
   for (int t = bid + warp * nact; t < T; t += nact * nwarps) {
     if (t < offset || t >= offset + n) continue;
     for (int p = lane; p < packs; p += 32) {
-      const uint64_t off = a.partial_off + (uint64_t)t * row_bytes + (uint64_t)p * 16;
+      const uint64_t off = partial_off + (uint64_t)t * row_bytes + (uint64_t)p * 16;
       uint4 v;
       if (c.transport == MCB_TRANSPORT_MULTIMEM) {
         v = mm_ld_reduce_bf16x8(c.heap_mc + off);

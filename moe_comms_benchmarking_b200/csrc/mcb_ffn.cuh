@@ -18,10 +18,16 @@
 //   * the gate/up matrix is stored interleaved (row 2i = gate row i, row 2i + 1 = up row i), so a
 //     128-row block yields 64 finished activations: the two values meet in neighbouring TMEM lanes
 //     and are exchanged with one shuffle;
-//   * weights arrive by TMA (128 rows x 64 columns per stage, 128-byte swizzle, no multicast), token
-//     rows by asynchronous 16-byte copies through the pair -> token list (the routing permute fused
-//     into the operand load) into the same swizzled K-major layout; the number of pipeline stages
-//     grows as the token tile shrinks (11 stages of 18 KB at N = 16, 4 of 48 KB at N = 256);
+//   * the weights are PRE-PACKED, once, into the image their tiles have in shared memory: tile
+//     (128-row block, 64-column block) is 16 KB of contiguous memory holding the 128 x 64 bf16 values
+//     in the K-major layout with 128-byte swizzle that the MMA descriptor expects, and the 16 tiles of
+//     a work unit follow one another.  A stage is then filled by ONE bulk copy (cp.async.bulk, no
+//     tensor map, no multicast) of a contiguous 16 KB range, so DRAM sees long sequential reads
+//     instead of 128 strided 128-byte pieces per tile;
+//   * token rows arrive by asynchronous 16-byte copies through the pair -> token list (the routing
+//     permute fused into the operand load) into the same swizzled K-major layout, eight neighbouring
+//     threads reading the 128 bytes of one row; the number of pipeline stages grows as the token tile
+//     shrinks (10 stages of 18 KB at N = 16, 4 of 48 KB at N = 256);
 //   * one elected thread issues tcgen05.mma; every mbarrier wait is bounded and reports through the
 //     status words.
 #pragma once
@@ -68,10 +74,34 @@ __device__ __forceinline__ FfnUnit ffn_unit(const McbFfnArgs& a, int u, int n1, 
   return r;
 }
 
+// Ask the L2 for the weights of this CTA's first a.prefetch_units units (the unit -> CTA assignment
+// is static and the weight addresses do not depend on the routing, so this can run before the
+// tokens have even arrived).  One warp; 16 KB per request.
+__device__ __forceinline__ void ffn_prefetch_weights(const McbFfnArgs& a) {
+  if (a.prefetch_units <= 0 || !a.w1 || !a.w2 || (threadIdx.x >> 5) != 0) return;
+  const int lane = threadIdx.x & 31;
+  const int H = a.hidden, I = a.intermediate;
+  const int n1 = 2 * I / kFfnRowsM, n2 = H / kFfnRowsM;
+  const int u1 = a.num_local_experts * n1, total = a.num_local_experts * (n1 + n2);
+  for (int k = 0; k < a.prefetch_units; ++k) {
+    const int u = blockIdx.x + k * gridDim.x;
+    if (u >= total) break;
+    const bool fc = u >= u1;
+    const int v = fc ? u - u1 : u;                 // 128-row block: its tiles are one contiguous range
+    const uint64_t bytes = (uint64_t)kFfnRowsM * (uint64_t)(fc ? I : H) * 2;
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(fc ? a.w2 : a.w1) + (uint64_t)v * bytes;
+    for (uint64_t off = (uint64_t)lane * 16384; off < bytes; off += 32ull * 16384) {
+      const uint32_t sz = bytes - off < 16384 ? (uint32_t)(bytes - off) : 16384u;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(base + off), "r"(sz) : "memory");
+    }
+  }
+}
+
 // Call from all kFfnThreads threads of every CTA of the grid; dynamic shared memory of at least
-// kFfnSmemBytes.  `w1_map` covers the interleaved gate/up matrix [E * 2I, H], `w2_map` the down
-// matrix [E * H, I] (both row-major bf16, boxes of 128 rows x 64 columns).
-__device__ __forceinline__ void ffn_device(const CUtensorMap* w1_map, const CUtensorMap* w2_map, const McbFfnArgs& a) {
+// kFfnSmemBytes.  a.w1 is the packed interleaved gate/up matrix (E * 2I rows, H columns), a.w2 the
+// packed down matrix (E * H rows, I columns): tile (row block v, column block kb) of a matrix with
+// KB column blocks starts at byte (v * KB + kb) * 16384.
+__device__ __forceinline__ void ffn_device(const McbFfnArgs& a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kFfnPipeBytes);
@@ -115,14 +145,14 @@ __device__ __forceinline__ void ffn_device(const CUtensorMap* w1_map, const CUte
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         const FfnUnit un = ffn_unit(a, u, n1, n2);
         if (un.rows <= 0) continue;
-        const CUtensorMap* map = un.fc ? w2_map : w1_map;
         const int k_blocks = (un.fc ? I : H) / kFfnBlockK;
-        const int wrow = un.e * (un.fc ? H : 2 * I) + un.j * kFfnRowsM;
+        const long long v = (long long)un.e * (un.fc ? n2 : n1) + un.j;       // 128-row block of the matrix
+        const uint8_t* tiles = reinterpret_cast<const uint8_t*>(un.fc ? a.w2 : a.w1) + v * k_blocks * (long long)kFfnABytes;
         for (int c0 = 0; c0 < un.rows && ok; c0 += kFfnMaxN) {
           for (int kb = 0; kb < k_blocks; ++kb) {
             if (!(ok = mbar_wait(&empty[s], ph ^ 1u, ab, 11))) break;
             mbar_arrive_expect_tx(&full[s], kFfnABytes);
-            tma_load_2d(smem + s * stage_bytes, map, &full[s], kb * kFfnBlockK, wrow);
+            bulk_load(smem + s * stage_bytes, tiles + (long long)kb * kFfnABytes, kFfnABytes, &full[s]);
             if (++s == stages) { s = 0; ph ^= 1u; }
           }
         }
@@ -231,7 +261,10 @@ __device__ __forceinline__ void ffn_device(const CUtensorMap* w1_map, const CUte
     }
   } else {
     // ---------------- token-row producers: gather rows into the swizzled K-major B tile ----------------
-    const int t = threadIdx.x - 6 * 32;      // 0..127: rows t and t + 128 of the token tile
+    // Thread t copies 16-byte chunk (t & 7) of rows (t >> 3), (t >> 3) + 16, ...: the eight threads of a
+    // row read its 128 bytes as one line, and a warp's 32 chunks fill four whole shared-memory rows.
+    const int t = threadIdx.x - 6 * 32;      // 0..127
+    const int chunk = t & 7, rbase = t >> 3;
     int s = 0; uint32_t ph = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
@@ -245,6 +278,7 @@ __device__ __forceinline__ void ffn_device(const CUtensorMap* w1_map, const CUte
           const uint64_t t0 = now_ns();
           while (ld_acquire_gpu_i32(&a.ffn_done[un.e]) < 4 * n1) {
             if (*ab.flag) break;
+            if (ab.status && *reinterpret_cast<volatile uint32_t*>(ab.status) != 0u) { *ab.flag = 1; break; }
             if (now_ns() - t0 > ab.timeout_ns) {
               *ab.flag = 1;
               if (ab.status && atomicCAS(ab.status, 0u, (uint32_t)MCB_GEMM_ERR_TIMEOUT) == 0u) {
@@ -257,30 +291,25 @@ __device__ __forceinline__ void ffn_device(const CUtensorMap* w1_map, const CUte
         __syncwarp();
       }
       const uint64_t src_row_bytes = un.fc ? (uint64_t)I * 2 : a.x_row_bytes;
+      const uint8_t* src_base = reinterpret_cast<const uint8_t*>(un.fc ? a.act : a.x) + chunk * 16;
       for (int c0 = 0; c0 < un.rows && ok; c0 += kFfnMaxN) {
         const int n = un.rows - c0 < kFfnMaxN ? un.rows - c0 : kFfnMaxN;
-        const uint8_t* src[2];
-        bool live[2];
+        // source rows of this thread's rows of the tile (up to 16 of them)
+        long long srow[kFfnMaxN / 16];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int r = t + h * 128;
-          live[h] = r < n;
-          long long srow = 0;
-          if (live[h]) srow = un.fc ? (long long)un.row0 + c0 + r : (long long)a.pair_token[un.row0 + c0 + r];
-          src[h] = reinterpret_cast<const uint8_t*>(un.fc ? a.act : a.x) + srow * src_row_bytes;
+        for (int i = 0; i < kFfnMaxN / 16; ++i) {
+          const int r = rbase + 16 * i;
+          srow[i] = 0;
+          if (r < n) srow[i] = un.fc ? (long long)un.row0 + c0 + r : (long long)a.pair_token[un.row0 + c0 + r];
         }
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!(ok = mbar_wait(&empty[s], ph ^ 1u, ab, 16))) break;
           uint8_t* sb = smem + s * stage_bytes + kFfnABytes;
+          const uint8_t* g = src_base + (long long)kb * (kFfnBlockK * 2);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (live[h]) {
-              const int r = t + h * 128;
-              uint8_t* dst = sb + r * 128;
-              const uint8_t* g = src[h] + (long long)kb * (kFfnBlockK * 2);
-#pragma unroll
-              for (int c = 0; c < 8; ++c) cp_async_16(dst + ((c ^ (r & 7)) << 4), g + c * 16);
-            }
+          for (int i = 0; i < kFfnMaxN / 16; ++i) {
+            const int r = rbase + 16 * i;
+            if (r < n) cp_async_16(sb + r * 128 + ((chunk ^ (r & 7)) << 4), g + srow[i] * (long long)src_row_bytes);
           }
           cp_async_arrive_noinc(&full[s]);     // arrives when this thread's copies have landed
           if (++s == stages) { s = 0; ph ^= 1u; }

@@ -46,9 +46,14 @@ typedef struct {
   int32_t num_local_experts;
   int32_t hidden;              // multiple of 128
   int32_t intermediate;        // multiple of 64
-  int32_t reserved0;
+  // The whole-layer kernel can ask the L2 for the weights of each CTA's first `prefetch_units` work units
+  // (256 KB each at K = 1024) before its dispatch and routing phases, whose duration would otherwise be
+  // idle time of the memory system (0 = off).
+  int32_t prefetch_units;
   uint32_t* status;
   uint64_t timeout_ns;
+  const void* w1;              // packed interleaved gate/up matrix (E * 2I rows, hidden columns), see mcb_ffn.cuh
+  const void* w2;              // packed down matrix (E * hidden rows, I columns)
 } McbFfnArgs;
 
 // Routing of the gathered tokens to this rank's experts.
@@ -91,6 +96,11 @@ typedef struct {
   int32_t topk;
   int32_t cap;                 // per-rank capacity
   int32_t site;
+  // Bytes between two copies of the partial-sum buffer (0 = one copy).  With two, a caller that runs
+  // layers back to back alternates between them, so a rank that is already writing the partial sums of
+  // the next layer cannot disturb a peer that is still reducing this one (the barrier inside every
+  // combine keeps ranks within one layer of each other).
+  uint64_t partial_par_stride;
 } McbCombineArgs;
 
 #ifdef __cplusplus
@@ -99,11 +109,8 @@ typedef struct {
 
 #ifdef MCB_WITH_LAYER_ARGS
 // Everything one MoE layer needs, as ONE kernel parameter (or one element of a device array when
-// several ranks are emulated inside one launch): the two weight tensor maps first (64-byte aligned),
-// then the context and the argument blocks of the four phases.
+// several ranks are emulated inside one launch): the context and the argument blocks of the four phases.
 typedef struct alignas(64) {
-  CUtensorMap w1;              // interleaved gate/up matrix [E * 2I, H]
-  CUtensorMap w2;              // down matrix [E * H, I]
   McbCtx ctx;
   McbAgvArgs agv;
   McbRouteArgs route;

@@ -54,6 +54,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     for (int i = 0; i < 32; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*ab.flag) return false;
+    // Once any kernel on this rank has recorded an error, later waits give up at once, so the rest
+    // of a captured multi-layer step drains quickly instead of timing out launch by launch.
+    if (ab.status && *reinterpret_cast<volatile uint32_t*>(ab.status) != 0u) {
+      *ab.flag = 1;
+      return false;
+    }
     if (now_ns() - t0 > ab.timeout_ns) {
       *ab.flag = 1;
       if (ab.status && atomicCAS(ab.status, 0u, (uint32_t)MCB_GEMM_ERR_TIMEOUT) == 0u) {
@@ -70,6 +76,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       :: "r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// Bulk copy of a contiguous, 16-byte aligned range of global memory into shared memory (no tensor
+// map, no multicast); completion is counted in bytes on the mbarrier.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :: "r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
 // Asynchronous 16-byte global -> shared copy (L2 only), and "arrive on this mbarrier once all

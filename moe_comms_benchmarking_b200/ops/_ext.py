@@ -141,25 +141,23 @@ class McbFfnArgs(C.Structure):
     _fields_ = [
         ("x", _vp), ("x_row_bytes", _u64), ("pair_token", _vp), ("pair_prob", _vp), ("expert_offset", _vp),
         ("max_rows", _vp), ("act", _vp), ("y", _vp), ("ffn_done", _vp),
-        ("num_local_experts", _i32), ("hidden", _i32), ("intermediate", _i32), ("reserved0", _i32),
-        ("status", _vp), ("timeout_ns", _u64),
+        ("num_local_experts", _i32), ("hidden", _i32), ("intermediate", _i32), ("prefetch_units", _i32),
+        ("status", _vp), ("timeout_ns", _u64), ("w1", _vp), ("w2", _vp),
     ]
 
 
 class McbCombineArgs(C.Structure):
     _fields_ = [
         ("y", _vp), ("pair_pos", _vp), ("partial_off", _u64), ("out", _vp), ("n_local", _vp), ("step_meta", _vp),
-        ("hidden", _i32), ("topk", _i32), ("cap", _i32), ("site", _i32),
+        ("hidden", _i32), ("topk", _i32), ("cap", _i32), ("site", _i32), ("partial_par_stride", _u64),
     ]
 
 
 class McbLayerArgs(C.Structure):
-    """One MoE layer as one kernel parameter: two 128-byte tensor maps, then the context and the
-    argument blocks of the four phases (64-byte aligned as a whole)."""
-    _pack_ = 0
+    """One MoE layer as one kernel parameter: the context and the argument blocks of the four
+    phases (64-byte aligned as a whole)."""
     _fields_ = [
-        ("w1", C.c_uint8 * 128), ("w2", C.c_uint8 * 128), ("ctx", McbCtx), ("agv", McbAgvArgs),
-        ("route", McbRouteArgs), ("ffn", McbFfnArgs), ("cmb", McbCombineArgs),
+        ("ctx", McbCtx), ("agv", McbAgvArgs), ("route", McbRouteArgs), ("ffn", McbFfnArgs), ("cmb", McbCombineArgs),
     ]
 
 

@@ -23,40 +23,65 @@ NUM_SMS = 148
 BLOCK_M = 128
 
 
+def _swizzle_index(device) -> torch.Tensor:
+    """index[r, c'] = c' ^ (r % 8): which 16-byte chunk of row r sits at position c' of the swizzled row."""
+    r = torch.arange(128, device=device).view(128, 1) % 8
+    return torch.arange(8, device=device).view(1, 8) ^ r
+
+
+def pack_weight_tiles(w: torch.Tensor) -> torch.Tensor:
+    """``[E, R, K]`` row-major bf16 -> ``[E, R/128, K/64, 128, 64]``: every (128-row, 64-column) tile as 16 KB of
+    contiguous memory in the K-major shared-memory image with 128-byte swizzle (16-byte chunk c of row r of a
+    tile is stored at chunk position c ^ (r % 8)), the tiles of a 128-row block one after the other."""
+    E, R, K = w.shape
+    if R % 128 or K % 64:
+        raise ValueError("rows must be a multiple of 128 and columns a multiple of 64")
+    t = w.view(E, R // 128, 128, K // 64, 8, 8).permute(0, 1, 3, 2, 4, 5)      # [E, RB, KB, 128, chunk, 8]
+    idx = _swizzle_index(w.device).view(1, 1, 1, 128, 8, 1).expand(E, R // 128, K // 64, 128, 8, 8)
+    return torch.gather(t, 4, idx).contiguous().view(E, R // 128, K // 64, 128, 64)
+
+
+def unpack_weight_tiles(p: torch.Tensor) -> torch.Tensor:
+    """Inverse of ``pack_weight_tiles`` (the swizzle is its own inverse)."""
+    E, RB, KB = p.shape[:3]
+    t = p.view(E, RB, KB, 128, 8, 8)
+    idx = _swizzle_index(p.device).view(1, 1, 1, 128, 8, 1).expand(E, RB, KB, 128, 8, 8)
+    return torch.gather(t, 4, idx).permute(0, 1, 3, 2, 4, 5).contiguous().view(E, RB * 128, KB * 64)
+
+
 class ExpertWeights:
-    """bf16 weights of this rank's experts and their TMA tensor maps.
+    """bf16 weights of this rank's experts: random N(0, std^2), generated as gate/up ``[E_loc, 2*I, H]`` (gate rows
+    first) and down ``[E_loc, H, I]``, kept in the form the kernels stream:
 
-    ``w_down`` is ``[E_loc, H, I]``.  The gate/up matrix exists in one of two layouts of the same
-    values (random N(0, std^2), generated as ``[E_loc, 2*I, H]`` with the gate rows first):
+    * ``layout="packed"`` (default), for the weights-as-M FFN kernel: the gate/up rows interleaved (row ``2i`` =
+      gate row ``i``, row ``2i + 1`` = up row ``i``, so a 128-row block holds 64 finished activations) and both
+      matrices packed tile by tile into their shared-memory image (``pack_weight_tiles``): ``w1``, ``w2``;
+    * ``layout="split"``, for the tokens-as-rows GEMM kernels: row-major matrices with TMA tensor maps.
 
-    * ``layout="interleaved"`` (default): row ``2i`` is gate row ``i`` and row ``2i + 1`` is up row
-      ``i``, which is what the weights-as-M FFN kernel streams (a 128-row block then holds 64
-      finished activations);
-    * ``layout="split"``: gate rows then up rows, for the tokens-as-rows GEMM kernels.
-
-    ``w_gate_up`` always returns the split layout (computed on demand from the interleaved one),
-    which is what the CPU oracle takes."""
+    ``w_gate_up`` / ``w_down`` always return the plain row-major matrices (unpacked on demand), which is what the
+    CPU oracle takes."""
 
     def __init__(self, num_local_experts: int, hidden: int, intermediate: int, device, seed: int = 0, std: float = 0.02,
-                 layout: str = "interleaved"):
+                 layout: str = "packed"):
         if hidden % 256 or intermediate % 128:
             raise ValueError("hidden must be a multiple of 256 and intermediate a multiple of 128")
-        if layout not in ("interleaved", "split"):
-            raise ValueError(f"unknown gate/up layout {layout!r}")
+        if layout not in ("packed", "split"):
+            raise ValueError(f"unknown weight layout {layout!r}")
         g = torch.Generator(device=device).manual_seed(seed)
         self.num_local_experts, self.hidden, self.intermediate = num_local_experts, hidden, intermediate
         self.layout = layout
         split = (torch.randn(num_local_experts, 2 * intermediate, hidden, device=device, generator=g,
                              dtype=torch.float32) * std).to(torch.bfloat16)
-        self.w_down = (torch.randn(num_local_experts, hidden, intermediate, device=device, generator=g,
-                                   dtype=torch.float32) * std).to(torch.bfloat16)
-        if layout == "interleaved":
-            self.w1 = self.interleave(split)
-            del split
+        down = (torch.randn(num_local_experts, hidden, intermediate, device=device, generator=g,
+                            dtype=torch.float32) * std).to(torch.bfloat16)
+        if layout == "packed":
+            self.w1 = pack_weight_tiles(self.interleave(split))
+            self.w2 = pack_weight_tiles(down)
+            del split, down
         else:
-            self.w1 = split
-        self.map_w1 = make_weight_tmap(self.w1.view(-1, hidden))
-        self.map_down = make_weight_tmap(self.w_down.view(-1, intermediate))
+            self.w1, self.w2 = split, down
+            self.map_w1 = make_weight_tmap(self.w1.view(-1, hidden))
+            self.map_down = make_weight_tmap(self.w2.view(-1, intermediate))
 
     @staticmethod
     def interleave(split: torch.Tensor) -> torch.Tensor:
@@ -68,8 +93,13 @@ class ExpertWeights:
     def w_gate_up(self) -> torch.Tensor:
         if self.layout == "split":
             return self.w1
-        E, two_i, H = self.w1.shape
-        return self.w1.view(E, two_i // 2, 2, H).transpose(1, 2).contiguous().view(E, two_i, H)
+        il = unpack_weight_tiles(self.w1)
+        E, two_i, H = il.shape
+        return il.view(E, two_i // 2, 2, H).transpose(1, 2).contiguous().view(E, two_i, H)
+
+    @property
+    def w_down(self) -> torch.Tensor:
+        return self.w2 if self.layout == "split" else unpack_weight_tiles(self.w2)
 
     @property
     def map_gate_up(self):
@@ -78,7 +108,7 @@ class ExpertWeights:
         return self.map_w1
 
     def bytes(self) -> int:
-        return (self.w1.numel() + self.w_down.numel()) * 2
+        return (self.w1.numel() + self.w2.numel()) * 2
 
 
 def make_weight_tmap(w2d: torch.Tensor):
@@ -187,14 +217,17 @@ class ExpertCombinePlan:
         if y.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or hidden % 8:
             raise ValueError("y and out must be bf16 with hidden a multiple of 8")
         _check_heap_tensor(heap, partial, "combine partial sums")
-        if partial.nbytes < cap * heap.world * hidden * 2:
-            raise ValueError("partial-sum buffer smaller than [cap * world, hidden]")
+        rows = cap * heap.world
+        two = partial.tensor.dim() == 3         # [2, cap * world, hidden]: alternate copies, layer by layer
+        if (two and (partial.tensor.shape[0] != 2 or partial.tensor.shape[1] < rows)) or partial.nbytes < rows * hidden * 2:
+            raise ValueError("partial-sum buffer must be [cap * world, hidden] or [2, cap * world, hidden]")
         self.heap, self.grid, self.threads = heap, grid, threads
         self._keep = (y, route, partial, out, n_local, step_meta)
         a = _ext.McbCombineArgs()
         a.y, a.pair_pos, a.partial_off, a.out = y.data_ptr(), route.pair_pos.data_ptr(), partial.offset, out.data_ptr()
         a.n_local, a.step_meta = n_local.data_ptr(), step_meta.data_ptr()
         a.hidden, a.topk, a.cap, a.site = hidden, route.topk, int(cap), int(site)
+        a.partial_par_stride = partial.nbytes // 2 if two else 0
         self.args = a
 
     def launch(self, pdl: bool = False, stream=None):
@@ -256,10 +289,10 @@ class ExpertFfnPlan:
     (``expert_ffn_kernel``): weights are the M = 128 operand, an expert's tokens the small N."""
 
     def __init__(self, weights: ExpertWeights, route: RouteBuffers, x: torch.Tensor, act: torch.Tensor, y: torch.Tensor,
-                 status: torch.Tensor | None = None, grid: int = NUM_SMS, timeout_s: float = 2.0):
+                 status: torch.Tensor | None = None, grid: int = NUM_SMS, timeout_s: float = 2.0, prefetch_units: int = 0):
         H, I = weights.hidden, weights.intermediate
-        if weights.layout != "interleaved":
-            raise ValueError("the FFN kernel streams the interleaved gate/up layout")
+        if weights.layout != "packed":
+            raise ValueError("the FFN kernel streams the packed weight layout")
         for t, cols, what in ((x, H, "x"), (act, I, "act"), (y, H, "y")):
             if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.shape[-1] != cols:
                 raise ValueError(f"{what} must be contiguous bf16 with {cols} columns")
@@ -276,12 +309,13 @@ class ExpertFfnPlan:
         a.act, a.y, a.ffn_done = act.data_ptr(), y.data_ptr(), route.ffn_done.data_ptr()
         a.num_local_experts, a.hidden, a.intermediate = weights.num_local_experts, H, I
         a.status, a.timeout_ns = _ext.ptr(status), int(timeout_s * 1e9)
+        # only the whole-layer kernel prefetches (during its dispatch and routing phases)
+        a.prefetch_units, a.w1, a.w2 = int(prefetch_units), weights.w1.data_ptr(), weights.w2.data_ptr()
         self.args = a
 
     def launch(self, pdl: bool = False, stream=None):
         lib = _ext.require()
-        _ext.check(lib.mcb_launch_expert_ffn(C.c_void_p(self.weights.map_w1[1]), C.c_void_p(self.weights.map_down[1]),
-                                             C.byref(self.args), self.grid, int(pdl), _ext.stream_handle(stream)),
+        _ext.check(lib.mcb_launch_expert_ffn(C.byref(self.args), self.grid, int(pdl), _ext.stream_handle(stream)),
                    "expert_ffn")
 
 
@@ -303,8 +337,6 @@ class MoeLayerPlan:
         ctx = self.heap.ctx()
         for s, f in enumerate(self.ffns):
             p = _ext.McbLayerArgs.from_address(self._addr + s * self._stride)
-            C.memmove(C.addressof(p.w1), f.weights.map_w1[1], 128)
-            C.memmove(C.addressof(p.w2), f.weights.map_down[1], 128)
             C.memmove(C.addressof(p.ctx), C.addressof(ctx), C.sizeof(_ext.McbCtx))
             C.memmove(C.addressof(p.agv), C.addressof(self.agv.args), C.sizeof(_ext.McbAgvArgs))
             C.memmove(C.addressof(p.route), C.addressof(self.route.args), C.sizeof(_ext.McbRouteArgs))

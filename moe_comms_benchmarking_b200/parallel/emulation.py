@@ -195,8 +195,6 @@ class EmuWorld:
         for r, d in enumerate(ranks):
             p = _ext.McbLayerArgs()
             w, route = d["weights"], d["route"]
-            C.memmove(C.addressof(p.w1), w.map_w1[1], 128)
-            C.memmove(C.addressof(p.w2), w.map_down[1], 128)
             C.memmove(C.addressof(p.ctx), C.addressof(self.ctxs[r]), C.sizeof(_ext.McbCtx))
             a = p.agv
             for i, (src, dst) in enumerate(zip(d["src"], d["dst"])):
@@ -222,10 +220,13 @@ class EmuWorld:
             ff.act, ff.y, ff.ffn_done = d["act"].data_ptr(), d["y"].data_ptr(), route.ffn_done.data_ptr()
             ff.num_local_experts, ff.hidden, ff.intermediate = w.num_local_experts, w.hidden, w.intermediate
             ff.status, ff.timeout_ns = self.status[r].data_ptr(), int(timeout_s * 1e9)
+            ff.w1, ff.w2 = w.w1.data_ptr(), w.w2.data_ptr()
             cm = p.cmb
             cm.y, cm.pair_pos, cm.partial_off, cm.out = d["y"].data_ptr(), route.pair_pos.data_ptr(), d["partial"].offset, d["out"].data_ptr()
             cm.n_local, cm.step_meta = d["n_local"].data_ptr(), d["step_meta"].data_ptr()
             cm.hidden, cm.topk, cm.cap, cm.site = w.hidden, topk, cap, _ext.SITE_FUSED_FC2
+            if d["partial"].tensor.dim() == 3:
+                cm.partial_par_stride = d["partial"].nbytes // 2
             blob[r * stride:r * stride + C.sizeof(p)] = bytes(p)
             if first is None:
                 first = p

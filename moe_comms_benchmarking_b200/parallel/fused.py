@@ -44,7 +44,7 @@ class FusedExpertDispatcher(Dispatcher):
                  threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto", ll_rows: int = -1,
                  num_layers: int = 88, weight_budget_gb: float = 64.0, weight_seed: int = 7,
                  fuse_combine: bool = True, fuse_dispatch: bool = True, coop_pdl: bool = False,
-                 layer_kernel: bool = True, device=None):
+                 layer_kernel: bool = True, prefetch_units: int = 0, device=None):
         super().__init__(cfg, group, device)
         self.heap, self._own_heap = heap, heap is None
         self.num_sms, self.threads, self.pdl, self.transport = int(num_sms), int(threads), bool(pdl), transport
@@ -54,6 +54,9 @@ class FusedExpertDispatcher(Dispatcher):
         self.coop_pdl = bool(coop_pdl)   # cooperative + programmatic dependent launch on the fused kernel
         self.fuse_dispatch = bool(fuse_dispatch)
         self.layer_kernel = bool(layer_kernel)
+        # work units (128 weight rows each) per CTA whose weights the layer kernel asks the L2 for while
+        # the dispatch and routing phases run
+        self.prefetch_units = int(prefetch_units)
         self.kernel_launches_per_step = lambda nl: 1 + (
             1 if self.layer_kernel else 5 - int(self.fuse_combine) - 2 * int(self.fuse_dispatch)) * nl
 
@@ -61,7 +64,7 @@ class FusedExpertDispatcher(Dispatcher):
     def heap_specs(cfg: Config, ll_rows: int = -1):
         g, H, K = max(cfg.global_cap, 1), cfg.hidden, cfg.topk
         ll = resolve_ll_rows(cfg, ll_rows)
-        return [([g, H], torch.bfloat16), ([g, K], torch.int64), ([g, K], torch.float32), ([g, H], torch.bfloat16),
+        return [([g, H], torch.bfloat16), ([g, K], torch.int64), ([g, K], torch.float32), ([2, g, H], torch.bfloat16),
                 ([max(agv_ll_stage_bytes(ll, [H * 2, K * 8, K * 4]), 16)], torch.uint8)]
 
     def build(self):
@@ -75,7 +78,8 @@ class FusedExpertDispatcher(Dispatcher):
         self.agv_h = h.alloc("fx_agv_h", [g, H], torch.bfloat16)
         self.agv_r = h.alloc("fx_agv_r", [g, K], torch.int64)
         self.agv_p = h.alloc("fx_agv_p", [g, K], torch.float32)
-        self.partial = h.alloc("fx_partial", [g, H], torch.bfloat16)
+        # per-token partial sums of this rank's experts, two copies used alternately layer by layer
+        self.partial = h.alloc("fx_partial", [2, g, H], torch.bfloat16)
         self.ll_agv = h.alloc("fx_ll_agv", [max(agv_ll_stage_bytes(self.ll_rows, [H * 2, K * 8, K * 4]), 16)], torch.uint8)
         self.in_hidden = torch.zeros(cap, H, dtype=torch.bfloat16, device=dev)
         self.in_routing = torch.zeros(cap, K, dtype=torch.int64, device=dev)
@@ -91,7 +95,7 @@ class FusedExpertDispatcher(Dispatcher):
         per_layer = E * 3 * H * I * 2
         sets = max(1, min(self.num_layers, int(self.weight_budget_gb * 2**30 // per_layer)))
         self.weights = [ExpertWeights(E, H, I, dev, seed=self.weight_seed * 100003 + s * 1009 + cfg.rank,
-                                      layout="interleaved" if self.layer_kernel else "split")
+                                      layout="packed" if self.layer_kernel else "split")
                         for s in range(sets)]
         st = h.status.view(torch.int32)
         self.meta_plan = MetadataPlan(h, self.n_local, self.step_metadata, cap)
@@ -104,7 +108,8 @@ class FusedExpertDispatcher(Dispatcher):
         self.combine_plan = ExpertCombinePlan(h, self.y, self.route, self.partial, self.out_buf, self.n_local,
                                               self.step_metadata, cap, grid=NUM_SMS)
         if self.layer_kernel:
-            self.ffn = [ExpertFfnPlan(w, self.route, self.agv_h.tensor, self.act, self.y, st) for w in self.weights]
+            self.ffn = [ExpertFfnPlan(w, self.route, self.agv_h.tensor, self.act, self.y, st,
+                                      prefetch_units=self.prefetch_units) for w in self.weights]
             self.layer_plan = MoeLayerPlan(h, self.agv_plan, self.route_plan, self.ffn, self.combine_plan, self.meta_plan)
         else:
             self.fc1 = [GroupedGemmPlan(_ext.GEMM_FC1, w.map_gate_up, self.route, self.agv_h.tensor, self.act, 2 * I, H, st)
@@ -204,26 +209,36 @@ class FusedExpertDispatcher(Dispatcher):
         return oracle.moe_layer(hidden.cpu(), topk_idx.cpu(), topk_w.cpu(), torch.cat(wgu), torch.cat(wd))
 
     def validate(self):
-        """One full layer against the CPU oracle at B = 2*ep and B = 1 (idle ranks)."""
+        """One full layer against the CPU oracle at B = 2*ep, at B = 1 (idle ranks) and, when the
+        capacity allows, at a realistic batch (up to 4096 tokens over all ranks, multi-block routing,
+        every expert busy) where a sample of this rank's tokens is compared."""
         from ..utils.inputs import make_inputs
         cfg, rank = self.cfg, self.cfg.rank
         results = []
-        for B in (cfg.ep_size * 2, 1):
+        cases = [cfg.ep_size * 2, 1]
+        big = min(self.cap * cfg.ep_size, 4096)
+        if big > 4 * cfg.ep_size:
+            cases.append(big)
+        for B in cases:
             counts = self._validation_counts(B)
             if max(counts) > self.cap:
                 continue
             h, i, w = make_inputs(cfg, B, self.device, n=counts[rank])
             self.setup_batch(h, i, w)
-            self.metadata()
-            self.layer(0)
-            self._sync_all()
+            for rep in range(2 if B == big else 1):     # twice at the large batch: counters must come back clean
+                self.metadata()
+                self.layer(0)
+                self._sync_all()
             if counts[rank]:
-                ref = self.reference_output(h, i, w)
-                got = self.out.float().cpu()
+                n = counts[rank]
+                sample = torch.arange(n) if n <= 16 else torch.arange(0, n, max(1, n // 8))[:8]
+                ref = self.reference_output(h[sample], i[sample], w[sample])
+                got = self.out[sample].float().cpu()
                 scale = float(ref.abs().max()) + 1e-6
                 err = float((got - ref).abs().max())
                 ok = err / scale < 0.05
-                detail = f"n={counts[rank]} max|got-ref|={err:.5f} ({100 * err / scale:.2f}% of {scale:.4f})"
+                detail = (f"n={n} ({sample.numel()} token(s) compared) max|got-ref|={err:.5f} "
+                          f"({100 * err / scale:.2f}% of {scale:.4f})")
             else:
                 ok, detail = True, "n=0 (idle rank still runs its experts on other ranks' tokens)"
             results.append((f"fused MoE layer vs oracle B={B:<4d}", bool(ok), detail))

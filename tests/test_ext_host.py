@@ -178,3 +178,78 @@ def test_capability_checks():
     assert ops.are_tensors_reduce_eligible(torch.zeros(2, 1024, dtype=torch.bfloat16))
     assert not ops.are_tensors_reduce_eligible(torch.zeros(2, 22))                 # 88-byte rows
     assert not ops.are_tensors_reduce_eligible(torch.zeros(2, 8, dtype=torch.int32))
+
+
+def test_step_plans_validate_arguments():
+    """Host-side checks of the persistent step plans (dense and all-to-all): shapes, capacities,
+    parity buffers, packet staging, fp8 tensor layout.  Nothing is launched."""
+    from moe_comms_benchmarking_b200.ops.a2a import A2AStepBuffers, A2AStepPlan, a2a_meta_row_bytes
+    from moe_comms_benchmarking_b200.ops.dense import (DenseStepPlan, agv_ll_stage_bytes, rsv_ll_stage_bytes,
+                                                       step_credit_bytes)
+    h = _heap(16 << 20)
+    cap, H, K = 8, 256, 6
+    n_local = torch.zeros(1, dtype=torch.int32)
+    meta8 = torch.zeros(8, dtype=torch.int32)
+    g2h = h.alloc("g2h", [2, cap, H], torch.bfloat16)
+    g2r = h.alloc("g2r", [2, cap, K], torch.int64)
+    rsv = h.alloc("rsv2", [cap, H], torch.bfloat16)
+    src_h = torch.zeros(cap, H, dtype=torch.bfloat16)
+    src_r = torch.zeros(cap, K, dtype=torch.int64)
+    out = torch.zeros(cap, H, dtype=torch.bfloat16)
+    p = DenseStepPlan(h, [g2h, g2r], [src_h, src_r], out, rsv, n_local, meta8, cap, 88)
+    assert p.args.num_layers == 88 and p.args.dst_par_stride[0] == cap * H * 2 and p.args.ll_rows == 0
+    with pytest.raises(ValueError):      # step_meta too short
+        DenseStepPlan(h, [g2h], [src_h], out, rsv, n_local, torch.zeros(4, dtype=torch.int32), cap, 2)
+    with pytest.raises(ValueError):      # gathered buffer without the parity dimension
+        DenseStepPlan(h, [h.alloc("flat", [cap, H], torch.bfloat16)], [src_h], out, rsv, n_local, meta8, cap, 2)
+    with pytest.raises(ValueError):      # pipeline groups need one block per SM
+        DenseStepPlan(h, [g2h], [src_h], out, rsv, n_local, meta8, cap, 2, grid=296, groups=2)
+    st_a = h.alloc("st_a", [agv_ll_stage_bytes(4, [H * 2, K * 8])], torch.uint8)
+    st_r = h.alloc("st_r", [rsv_ll_stage_bytes(1, 4, cap, H * 2)], torch.uint8)
+    with pytest.raises(ValueError):      # packet mode without its credit region
+        DenseStepPlan(h, [g2h, g2r], [src_h, src_r], out, rsv, n_local, meta8, cap, 2, agv_ll_stage=st_a,
+                      rsv_ll_stage=st_r, ll_rows=4)
+    cr = h.alloc("cr", [step_credit_bytes(148)], torch.uint8)
+    p = DenseStepPlan(h, [g2h, g2r], [src_h, src_r], out, rsv, n_local, meta8, cap, 2, agv_ll_stage=st_a,
+                      rsv_ll_stage=st_r, ll_rows=4, credits=cr)
+    assert p.args.ll_rows == 4 and p.args.credit_off == cr.offset
+    # fp8 dispatch: uint8 rows + fp32 scales as a fourth tensor without a source
+    q = h.alloc("q8", [2, cap, H], torch.uint8)
+    sc = h.alloc("sc8", [2, cap, H // 128], torch.float32)
+    g2p = h.alloc("g2p", [2, cap, K], torch.float32)
+    src_p = torch.zeros(cap, K, dtype=torch.float32)
+    p = DenseStepPlan(h, [q, g2r, g2p, sc], [src_h, src_r, src_p, None], out, rsv, n_local, meta8, cap, 2, fp8_hidden=H)
+    assert p.args.fp8_hidden == H and p.args.row_bytes[0] == H and p.args.row_bytes[3] == H // 128 * 4 and p.args.src[3] is None
+    with pytest.raises(ValueError):
+        DenseStepPlan(h, [g2h, g2r, g2p, sc], [src_h, src_r, src_p, None], out, rsv, n_local, meta8, cap, 2, fp8_hidden=H)
+    # all-to-all step
+    assert a2a_meta_row_bytes(22) == 192 and a2a_meta_row_bytes(8) == 80
+    for fp8 in (False, True):
+        b = A2AStepBuffers(h, cap, H, K, fp8, prefix=f"t{int(fp8)}")
+        assert b.recv_meta.tensor.shape == (2, 1, cap, a2a_meta_row_bytes(K))
+        p = A2AStepPlan(h, b, src_h, src_r, src_p, out, n_local, meta8, 16, 88)
+        assert p.args.x_par_stride == b.recv_x.nbytes // 2 and p.args.fp8 == int(fp8) and p.args.meta_row_bytes == 64
+        assert (p.args.y_off == p.args.recv_x_off) == (not fp8)
+        with pytest.raises(ValueError):
+            A2AStepPlan(h, b, src_h[:4], src_r, src_p, out, n_local, meta8, 16, 88)
+    st, tok, ids, wts = b.meta_fields(0, 0, 3)
+    assert st.shape == (3,) and ids.shape == (3, K) and wts.dtype == torch.float32
+
+
+def test_weight_tile_packing_round_trip():
+    """The pre-packed weight layout: tile (row block, column block) is 16 KB of contiguous memory in the
+    swizzled K-major shared-memory image; packing and unpacking are inverse, and chunk c of row r of a
+    tile sits at chunk position c ^ (r % 8)."""
+    from moe_comms_benchmarking_b200.ops.experts import ExpertWeights, pack_weight_tiles, unpack_weight_tiles
+    w = torch.randn(3, 256, 192).to(torch.bfloat16)
+    p = pack_weight_tiles(w)
+    assert p.shape == (3, 2, 3, 128, 64) and p.is_contiguous()
+    assert torch.equal(unpack_weight_tiles(p), w)
+    for (e, rb, kb, r, c) in ((0, 0, 0, 0, 0), (1, 1, 2, 5, 3), (2, 0, 1, 127, 7), (2, 1, 0, 9, 6)):
+        pos = c ^ (r % 8)
+        assert torch.equal(p[e, rb, kb, r, pos * 8:pos * 8 + 8], w[e, rb * 128 + r, kb * 64 + c * 8:kb * 64 + c * 8 + 8])
+    split = torch.arange(2 * 8 * 4, dtype=torch.float32).view(2, 8, 4)
+    il = ExpertWeights.interleave(split)
+    assert torch.equal(il[:, 0::2], split[:, :4]) and torch.equal(il[:, 1::2], split[:, 4:])
+    with pytest.raises(ValueError):
+        pack_weight_tiles(torch.zeros(1, 100, 64, dtype=torch.bfloat16))

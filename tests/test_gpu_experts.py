@@ -103,7 +103,8 @@ def test_expert_ffn_weights_as_m_against_oracle(world1, T, E, K, H, I, grid):
     ntok = torch.tensor([T], dtype=torch.int32, device=DEV)
     route = RouteBuffers(cap, K, E, DEV)
     weights = ExpertWeights(E, H, I, DEV, seed=5, std=0.05)
-    assert torch.equal(ExpertWeights.interleave(weights.w_gate_up), weights.w1)
+    from moe_comms_benchmarking_b200.ops.experts import pack_weight_tiles
+    assert torch.equal(pack_weight_tiles(ExpertWeights.interleave(weights.w_gate_up)), weights.w1)
     act = torch.zeros(route.max_pairs, I, dtype=torch.bfloat16, device=DEV)
     y = torch.zeros(route.max_pairs, H, dtype=torch.bfloat16, device=DEV)
     rp = RoutePlan(route, idxs, ws, ntok, expert_begin=0, status=heap.status, grid=7)
@@ -152,7 +153,7 @@ def test_moe_layer_kernel_emulated_ranks(lib, W, B, ll_rows):
     cap, g = max(counts), max(counts) * W
     w = EmuWorld(W, 8 << 20, DEV)
     dst = [w.alloc([g, H], torch.bfloat16), w.alloc([g, K], torch.int64), w.alloc([g, K], torch.float32)]
-    partial = w.alloc([g, H], torch.bfloat16)
+    partial = w.alloc([2, g, H], torch.bfloat16)
     ll = w.alloc([max(16, agv_ll_stage_bytes(ll_rows, [H * 2, K * 8, K * 4]))], torch.uint8)
     gen = torch.Generator(device=DEV).manual_seed(41)
     ranks = []

@@ -46,11 +46,36 @@ def test_tensor_parallel_collectives_multi_gpu(transport):
     assert f"# SELFTEST PASSED (all {n} ranks" in res.stdout
 
 
-def test_fused_experts_validate_multi_gpu():
+def test_fp8_dispatch_on_both_paths_multi_gpu():
+    """1 x 128 block-scaled e4m3 dispatch on the dense path and on the all-to-all path, each against its
+    own checks and against each other (cross-impl [a2a-fp8=dense-fp8])."""
+    n = _ngpu()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    n = 4 if n >= 4 else 2
+    res = _torchrun(n, ["run.py", "--impl", "both", "--validate", "--dispatch-dtype", "fp8"])
+    assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-4000:]
+    assert f"# VALIDATION PASSED (all {n} ranks)" in res.stdout
+    assert "cross-impl [a2a-fp8=dense-fp8]" in res.stdout
+
+
+@pytest.mark.parametrize("extra", [[], ["--no-layer-kernel"], ["--transport", "p2p"]])
+def test_fused_experts_validate_multi_gpu(extra):
     n = _ngpu()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     res = _torchrun(2, ["run.py", "--impl", "fused", "--validate", "--num-experts", "64", "--topk", "6",
+                        "--hidden", "512", "--intermediate", "256"] + extra)
+    assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-4000:]
+    assert "# VALIDATION PASSED (all 2 ranks)" in res.stdout
+
+
+def test_extended_baseline_validate_multi_gpu():
+    """NCCL + library GEMMs with real experts (the extended baseline of the fused path) against the oracle."""
+    n = _ngpu()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    res = _torchrun(2, ["run.py", "--impl", "nccl", "--expert", "swiglu", "--validate", "--num-experts", "64", "--topk", "6",
                         "--hidden", "512", "--intermediate", "256"])
     assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-4000:]
     assert "# VALIDATION PASSED (all 2 ranks)" in res.stdout
