@@ -96,6 +96,23 @@ def main(argv=None):
                         p.launch()
             torch.cuda.synchronize()
             times[name] = sorted(s.elapsed_time(e) * 1e3 for s, e in evs)[len(evs) // 2]
+        # back-to-back launches of the weight-streaming kernels (no host gap, no flush needed: a layer's
+        # weights are several times the L2): the kernel time without launch latency
+        b2b = {}
+        for name in ("fc1", "fc2", "ffn"):
+            if only and name not in only:
+                b2b[name] = float("nan")
+                continue
+            reps = max(args.iters, 5)
+            plans[name].launch()
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(reps):
+                plans[name].launch()
+            e.record()
+            torch.cuda.synchronize()
+            b2b[name] = s.elapsed_time(e) * 1e3 / reps
         heap.check_status()
         pairs = int(route.expert_offset[E])
         tiles = int(route.num_m_tiles)
@@ -111,7 +128,8 @@ def main(argv=None):
               f"{100 * frac(times['fc2'], w2 + pairs * (H + I) * 2, f2):4.0f}%) | "
               f"ffn (gate/up + down, weights as M, one launch) {times['ffn']:7.1f}us ({(w1 + w2) / times['ffn'] / 1e3:6.0f} GB/s weights, "
               f"{100 * frac(times['ffn'], w1 + w2 + pairs * (H + 2 * I + H) * 2, f1 + f2):4.0f}% of roofline) | "
-              f"combine {times['combine']:7.1f}us", flush=True)
+              f"combine {times['combine']:7.1f}us | back to back: fc1 {b2b['fc1']:6.1f} fc2 {b2b['fc2']:6.1f} "
+              f"ffn {b2b['ffn']:6.1f}us ({(w1 + w2) / b2b['ffn'] / 1e3:5.0f} GB/s)", flush=True)
 
 
 if __name__ == "__main__":

@@ -37,7 +37,6 @@ __global__ void __launch_bounds__(kFfnThreads, 1)
 moe_layer_kernel(const __grid_constant__ McbLayerArgs p_, const McbLayerArgs* eargs) {
   const McbLayerArgs& p = EMU ? eargs[blockIdx.y] : p_;
   const McbCtx& c = p.ctx;
-  ffn_prefetch_weights(p.ffn);           // weights do not change between launches: no need to wait for the predecessor
   uint32_t ll_launch = 0;
   agv_device<MCB_SITE_FC1_FUSED>(c, p.agv, ll_launch);      // waits for the previous kernel first
   // The arrival counter is back at zero whenever a launch has ended (its last block resets it).
@@ -76,7 +75,7 @@ static bool configure_ffn_kernels() {
 static int check_ffn_args(const McbFfnArgs* a) {
   if (!a || !a->x || !a->pair_token || !a->expert_offset || !a->max_rows || !a->act || !a->y || !a->ffn_done) return 1;
   if (!a->w1 || !a->w2 || (reinterpret_cast<uintptr_t>(a->w1) & 15) || (reinterpret_cast<uintptr_t>(a->w2) & 15)) return 1;
-  if (a->num_local_experts < 1 || a->hidden < 128 || a->hidden % 128 || a->intermediate < 64 || a->intermediate % 64) return 1;
+  if (a->num_local_experts < 1 || a->hidden < 128 || a->hidden % 128 || a->intermediate < 128 || a->intermediate % 128) return 1;
   if (a->x_row_bytes & 15) return 1;
   return 0;
 }

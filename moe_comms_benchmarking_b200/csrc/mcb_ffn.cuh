@@ -26,8 +26,11 @@
 //     instead of 128 strided 128-byte pieces per tile;
 //   * token rows arrive by asynchronous 16-byte copies through the pair -> token list (the routing
 //     permute fused into the operand load) into the same swizzled K-major layout, eight neighbouring
-//     threads reading the 128 bytes of one row; the number of pipeline stages grows as the token tile
-//     shrinks (10 stages of 18 KB at N = 16, 4 of 48 KB at N = 256);
+//     threads reading the 128 bytes of one row; a pipeline stage holds two 64-column blocks (one 32 KB
+//     bulk copy: with 16 KB stages the per-stage work of the single MMA-issuing thread - barrier wait,
+//     proxy fence, descriptors, commit - limited the weight stream), and the number of stages grows as
+//     the token tile shrinks (5 stages of 36 KB at N = 16; tiles of more than 64 tokens go back to one
+//     block per stage, 4 stages of 48 KB at N = 256);
 //   * one elected thread issues tcgen05.mma; every mbarrier wait is bounded and reports through the
 //     status words.
 #pragma once
@@ -40,7 +43,8 @@ constexpr int kFfnRowsM = 128;              // weight rows per unit
 constexpr int kFfnBlockK = 64;              // 128 bytes of bf16
 constexpr int kFfnMaxN = 256;               // tokens per pass
 constexpr int kFfnMaxStages = 12;
-constexpr int kFfnABytes = kFfnRowsM * kFfnBlockK * 2;           // 16 KiB
+constexpr int kFfnMaxSub = 2;               // 64-column blocks per pipeline stage at small token tiles (one 32 KB bulk copy)
+constexpr int kFfnABytes = kFfnRowsM * kFfnBlockK * 2;           // 16 KiB per 64-column block
 constexpr int kFfnPipeBytes = 196 * 1024;
 constexpr int kFfnSmemBytes = kFfnPipeBytes + 1024 /*align*/ + 512 /*barriers*/;
 
@@ -74,34 +78,12 @@ __device__ __forceinline__ FfnUnit ffn_unit(const McbFfnArgs& a, int u, int n1, 
   return r;
 }
 
-// Ask the L2 for the weights of this CTA's first a.prefetch_units units (the unit -> CTA assignment
-// is static and the weight addresses do not depend on the routing, so this can run before the
-// tokens have even arrived).  One warp; 16 KB per request.
-__device__ __forceinline__ void ffn_prefetch_weights(const McbFfnArgs& a) {
-  if (a.prefetch_units <= 0 || !a.w1 || !a.w2 || (threadIdx.x >> 5) != 0) return;
-  const int lane = threadIdx.x & 31;
-  const int H = a.hidden, I = a.intermediate;
-  const int n1 = 2 * I / kFfnRowsM, n2 = H / kFfnRowsM;
-  const int u1 = a.num_local_experts * n1, total = a.num_local_experts * (n1 + n2);
-  for (int k = 0; k < a.prefetch_units; ++k) {
-    const int u = blockIdx.x + k * gridDim.x;
-    if (u >= total) break;
-    const bool fc = u >= u1;
-    const int v = fc ? u - u1 : u;                 // 128-row block: its tiles are one contiguous range
-    const uint64_t bytes = (uint64_t)kFfnRowsM * (uint64_t)(fc ? I : H) * 2;
-    const uint8_t* base = reinterpret_cast<const uint8_t*>(fc ? a.w2 : a.w1) + (uint64_t)v * bytes;
-    for (uint64_t off = (uint64_t)lane * 16384; off < bytes; off += 32ull * 16384) {
-      const uint32_t sz = bytes - off < 16384 ? (uint32_t)(bytes - off) : 16384u;
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(base + off), "r"(sz) : "memory");
-    }
-  }
-}
-
 // Call from all kFfnThreads threads of every CTA of the grid; dynamic shared memory of at least
 // kFfnSmemBytes.  a.w1 is the packed interleaved gate/up matrix (E * 2I rows, H columns), a.w2 the
 // packed down matrix (E * H rows, I columns): tile (row block v, column block kb) of a matrix with
 // KB column blocks starts at byte (v * KB + kb) * 16384.
-__device__ __forceinline__ void ffn_device(const McbFfnArgs& a) {
+template <int NSUB>
+__device__ __forceinline__ void ffn_device_impl(const McbFfnArgs& a, const int n_slot) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kFfnPipeBytes);
@@ -129,13 +111,13 @@ __device__ __forceinline__ void ffn_device(const McbFfnArgs& a) {
   const int H = a.hidden, I = a.intermediate;
   const int n1 = 2 * I / kFfnRowsM, n2 = H / kFfnRowsM;
   const int total_units = a.num_local_experts * (n1 + n2);
-  // Token tile of this launch: the largest expert, rounded up to 16, at most kFfnMaxN per pass.
-  int max_rows = *a.max_rows;
-  if (max_rows < 1) max_rows = 1;
-  const int n_slot = max_rows >= kFfnMaxN ? kFfnMaxN : ((max_rows + 15) & ~15);
-  const int stage_bytes = kFfnABytes + n_slot * 128;
+  constexpr int nsub = NSUB;                                    // 64-column blocks per pipeline stage
+  const int b_sub_bytes = n_slot * 128;                         // token tile of one 64-column block
+  const int stage_bytes = nsub * (kFfnABytes + b_sub_bytes);    // [A block 0][A block 1][B block 0][B block 1]
   int stages = kFfnPipeBytes / stage_bytes;
   if (stages > kFfnMaxStages) stages = kFfnMaxStages;
+
+  constexpr uint32_t kStageA = (uint32_t)(nsub * kFfnABytes);     // weight bytes per stage: one bulk copy
 
   if (warp == 0) {
     // ---------------- TMA producer: 128 weight rows x 64 columns per stage ----------------
@@ -149,10 +131,10 @@ __device__ __forceinline__ void ffn_device(const McbFfnArgs& a) {
         const long long v = (long long)un.e * (un.fc ? n2 : n1) + un.j;       // 128-row block of the matrix
         const uint8_t* tiles = reinterpret_cast<const uint8_t*>(un.fc ? a.w2 : a.w1) + v * k_blocks * (long long)kFfnABytes;
         for (int c0 = 0; c0 < un.rows && ok; c0 += kFfnMaxN) {
-          for (int kb = 0; kb < k_blocks; ++kb) {
+          for (int kb = 0; kb < k_blocks; kb += nsub) {
             if (!(ok = mbar_wait(&empty[s], ph ^ 1u, ab, 11))) break;
-            mbar_arrive_expect_tx(&full[s], kFfnABytes);
-            bulk_load(smem + s * stage_bytes, tiles + (long long)kb * kFfnABytes, kFfnABytes, &full[s]);
+            mbar_arrive_expect_tx(&full[s], kStageA);
+            bulk_load(smem + s * stage_bytes, tiles + (long long)kb * kFfnABytes, kStageA, &full[s]);
             if (++s == stages) { s = 0; ph ^= 1u; }
           }
         }
@@ -174,15 +156,19 @@ __device__ __forceinline__ void ffn_device(const McbFfnArgs& a) {
           if (!(ok = mbar_wait(&tempty[acc], acc_ph ^ 1u, ab, 12))) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kFfnMaxN);
-          for (int kb = 0; kb < k_blocks; ++kb) {
+          for (int kb = 0; kb < k_blocks; kb += nsub) {
             if (!(ok = mbar_wait(&full[s], ph, ab, 13))) break;
             fence_proxy_async_smem();           // the token rows were written by cp.async, not by TMA
             tc_fence_after();
             const uint32_t sa = smem_u32(smem + s * stage_bytes);
-            const uint64_t da = make_sw128_desc(sa), db = make_sw128_desc(sa + kFfnABytes);
 #pragma unroll
-            for (int kk = 0; kk < kFfnBlockK / 16; ++kk)
-              umma_bf16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb | kk) != 0);
+            for (int sub = 0; sub < nsub; ++sub) {
+              const uint64_t da = make_sw128_desc(sa + sub * kFfnABytes);
+              const uint64_t db = make_sw128_desc(sa + nsub * kFfnABytes + sub * b_sub_bytes);
+#pragma unroll
+              for (int kk = 0; kk < kFfnBlockK / 16; ++kk)
+                umma_bf16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb | sub | kk) != 0);
+            }
             umma_commit(&empty[s]);
             if (++s == stages) { s = 0; ph ^= 1u; }
           }
@@ -302,14 +288,19 @@ __device__ __forceinline__ void ffn_device(const McbFfnArgs& a) {
           srow[i] = 0;
           if (r < n) srow[i] = un.fc ? (long long)un.row0 + c0 + r : (long long)a.pair_token[un.row0 + c0 + r];
         }
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = 0; kb < k_blocks; kb += nsub) {
           if (!(ok = mbar_wait(&empty[s], ph ^ 1u, ab, 16))) break;
-          uint8_t* sb = smem + s * stage_bytes + kFfnABytes;
+          uint8_t* sb = smem + s * stage_bytes + nsub * kFfnABytes;
           const uint8_t* g = src_base + (long long)kb * (kFfnBlockK * 2);
 #pragma unroll
           for (int i = 0; i < kFfnMaxN / 16; ++i) {
             const int r = rbase + 16 * i;
-            if (r < n) cp_async_16(sb + r * 128 + ((chunk ^ (r & 7)) << 4), g + srow[i] * (long long)src_row_bytes);
+            if (r < n) {
+              const uint8_t* gr = g + srow[i] * (long long)src_row_bytes;
+              uint8_t* dst = sb + r * 128 + ((chunk ^ (r & 7)) << 4);
+#pragma unroll
+              for (int sub = 0; sub < nsub; ++sub) cp_async_16(dst + sub * b_sub_bytes, gr + sub * (kFfnBlockK * 2));
+            }
           }
           cp_async_arrive_noinc(&full[s]);     // arrives when this thread's copies have landed
           if (++s == stages) { s = 0; ph ^= 1u; }
@@ -326,6 +317,17 @@ __device__ __forceinline__ void ffn_device(const McbFfnArgs& a) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+// Token tile of this launch: the largest expert, rounded up to 16, at most kFfnMaxN per pass.  Two
+// 64-column blocks per pipeline stage while the tile is small (the weight stream is then the limit and
+// the per-stage work of the MMA-issuing thread must be amortised), one when it is large.
+__device__ __forceinline__ void ffn_device(const McbFfnArgs& a) {
+  int max_rows = *a.max_rows;
+  if (max_rows < 1) max_rows = 1;
+  const int n_slot = max_rows >= kFfnMaxN ? kFfnMaxN : ((max_rows + 15) & ~15);
+  if (n_slot <= 128) ffn_device_impl<kFfnMaxSub>(a, n_slot);
+  else ffn_device_impl<1>(a, n_slot);
 }
 
 }  // namespace mcb

@@ -45,11 +45,8 @@ typedef struct {
   int32_t* ffn_done;           // [E_loc] quarter-blocks of gate/up finished (zeroed by the routing)
   int32_t num_local_experts;
   int32_t hidden;              // multiple of 128
-  int32_t intermediate;        // multiple of 64
-  // The whole-layer kernel can ask the L2 for the weights of each CTA's first `prefetch_units` work units
-  // (256 KB each at K = 1024) before its dispatch and routing phases, whose duration would otherwise be
-  // idle time of the memory system (0 = off).
-  int32_t prefetch_units;
+  int32_t intermediate;        // multiple of 128
+  int32_t reserved0;
   uint32_t* status;
   uint64_t timeout_ns;
   const void* w1;              // packed interleaved gate/up matrix (E * 2I rows, hidden columns), see mcb_ffn.cuh

@@ -141,7 +141,7 @@ class McbFfnArgs(C.Structure):
     _fields_ = [
         ("x", _vp), ("x_row_bytes", _u64), ("pair_token", _vp), ("pair_prob", _vp), ("expert_offset", _vp),
         ("max_rows", _vp), ("act", _vp), ("y", _vp), ("ffn_done", _vp),
-        ("num_local_experts", _i32), ("hidden", _i32), ("intermediate", _i32), ("prefetch_units", _i32),
+        ("num_local_experts", _i32), ("hidden", _i32), ("intermediate", _i32), ("reserved0", _i32),
         ("status", _vp), ("timeout_ns", _u64), ("w1", _vp), ("w2", _vp),
     ]
 

@@ -289,7 +289,7 @@ class ExpertFfnPlan:
     (``expert_ffn_kernel``): weights are the M = 128 operand, an expert's tokens the small N."""
 
     def __init__(self, weights: ExpertWeights, route: RouteBuffers, x: torch.Tensor, act: torch.Tensor, y: torch.Tensor,
-                 status: torch.Tensor | None = None, grid: int = NUM_SMS, timeout_s: float = 2.0, prefetch_units: int = 0):
+                 status: torch.Tensor | None = None, grid: int = NUM_SMS, timeout_s: float = 2.0):
         H, I = weights.hidden, weights.intermediate
         if weights.layout != "packed":
             raise ValueError("the FFN kernel streams the packed weight layout")
@@ -309,8 +309,7 @@ class ExpertFfnPlan:
         a.act, a.y, a.ffn_done = act.data_ptr(), y.data_ptr(), route.ffn_done.data_ptr()
         a.num_local_experts, a.hidden, a.intermediate = weights.num_local_experts, H, I
         a.status, a.timeout_ns = _ext.ptr(status), int(timeout_s * 1e9)
-        # only the whole-layer kernel prefetches (during its dispatch and routing phases)
-        a.prefetch_units, a.w1, a.w2 = int(prefetch_units), weights.w1.data_ptr(), weights.w2.data_ptr()
+        a.w1, a.w2 = weights.w1.data_ptr(), weights.w2.data_ptr()
         self.args = a
 
     def launch(self, pdl: bool = False, stream=None):

@@ -28,12 +28,13 @@ from .symm_heap import HeapTensor, SymmetricHeap, required_bytes
 
 
 def resolve_ll_rows(cfg: Config, ll_rows: int) -> int:
-    """Row limit of the low-latency packet mode.  ``-1`` picks 256 rows, the measured crossover
-    with the barrier + multicast mode on B200 (256 at EP=8, between 256 and 512 at EP=2 and EP=4)."""
+    """Row limit of the packet mode.  ``-1`` picks 512 rows: inside the persistent step kernel packets
+    beat barrier + multicast up to about that many rows in total (measured on B200: 0.57 against 1.00 ms per
+    88-layer step at 512 rows and EP=2; packets double the bytes, so the barrier mode wins from ~1000 rows)."""
     if cfg.ep_size <= 1:
         return 0
     if ll_rows < 0:
-        ll_rows = 256
+        ll_rows = 512
     return min(int(ll_rows), max(cfg.global_cap, 1))
 
 

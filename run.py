@@ -76,8 +76,6 @@ def parse_args(argv=None):
                    help="dense: one kernel per operation (1 + 2 x layers launches) instead of one per decode step")
     p.add_argument("--groups", type=int, default=1,
                    help="dense: pipeline groups of the persistent step kernel (1 = none)")
-    p.add_argument("--prefetch-units", type=int, default=0,
-                   help="fused: weight blocks per CTA requested from the L2 during the dispatch and routing phases")
     p.add_argument("--no-layer-kernel", action="store_true",
                    help="fused: the two-kernel form with tokens as the M operand instead of one kernel per layer")
     p.add_argument("--dense-num-sms", type=int, default=148, help="CTA cap of the dense kernels")
@@ -152,7 +150,7 @@ def build_dispatchers(names, cfg, group, args, device, sms_list):
                                              weight_budget_gb=args.weight_budget_gb,
                                              fuse_combine=not args.no_fuse_combine,
                                              fuse_dispatch=not args.no_fuse_dispatch, coop_pdl=args.coop_pdl,
-                                             layer_kernel=not args.no_layer_kernel, prefetch_units=args.prefetch_units))
+                                             layer_kernel=not args.no_layer_kernel))
         elif n == "nccl":
             from moe_comms_benchmarking_b200.parallel.nccl import NCCLDispatcher
             out.append(NCCLDispatcher(cfg, group))

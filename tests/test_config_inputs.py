@@ -93,7 +93,7 @@ def test_low_latency_limit_and_heap_sizing():
     from moe_comms_benchmarking_b200.parallel.dense import DenseDispatcher, resolve_ll_rows
     from moe_comms_benchmarking_b200.parallel.symm_heap import required_bytes
     assert resolve_ll_rows(Config(ep_size=1, per_rank_cap=64), -1) == 0           # nobody to talk to
-    assert resolve_ll_rows(Config(ep_size=8, per_rank_cap=1024), -1) == 256
+    assert resolve_ll_rows(Config(ep_size=8, per_rank_cap=1024), -1) == 512
     assert resolve_ll_rows(Config(ep_size=8, per_rank_cap=4), -1) == 32           # never above the capacity
     assert resolve_ll_rows(Config(ep_size=2, per_rank_cap=4096), 100) == 100
     assert resolve_ll_rows(Config(ep_size=2, per_rank_cap=4096), 0) == 0
