@@ -14,11 +14,18 @@
 //     buffers double buffered by layer parity (the barrier of layer l is the write-after-read fence
 //     for the readers of layer l - 1), and the 88 layers run inside one launch after one count
 //     exchange that also proves every rank has left the previous step;
-//   * optional 1 x 128 block-scaled e4m3 dispatch, quantised on the way out.
+//   * optional 1 x 128 block-scaled e4m3 dispatch, quantised on the way out;
+//   * packet mode for small steps: rows travel as 16-byte flagged packets, so a layer needs no fence
+//     and no barrier.  Every rank receives a one-packet header per token (routed to you or not), so a
+//     destination knows which rows to wait for; the destination's warp for that token unpacks the row
+//     into the ordinary receive buffers and sends the expert output straight back as packets, and the
+//     source sums them as they arrive.  All traffic of a token runs between the same block index on
+//     the ranks involved, and staging areas (two parities) are recycled on per-source credit words.
 // Every wait is bounded and reports through the status words.
 #include <cuda_runtime.h>
 
 #include "mcb_barrier.cuh"
+#include "mcb_dense.cuh"
 #include "mcb_fp8.cuh"
 #include "mcb_launch.h"
 #include "mcb_step.cuh"
@@ -42,6 +49,176 @@ __device__ __forceinline__ DestMask dest_mask(const McbCtx& c, const McbA2AStepA
 #pragma unroll
   for (int i = 0; i < 3; ++i) m.w[i] = __reduce_or_sync(0xffffffffu, m.w[i]);
   return m;
+}
+
+// ---- packet mode ------------------------------------------------------------------------------------
+struct LLShape {
+  int xdata;      // 8-byte words of a dispatched row (bf16: hidden / 4, e4m3: hidden / 8)
+  int scales;     // words of fp32 scales (e4m3 only: hidden / 256)
+  int meta;       // words of the packed metadata row
+  int xw;         // 1 header + xdata + scales + meta
+  int yw;         // words of an expert-output row (hidden / 4)
+};
+
+__device__ __forceinline__ uint64_t ll_x_slot(const McbA2AStepArgs& a, const LLShape& s, int world, uint32_t par, int src,
+                                              int t, int word) {
+  return a.ll_x_off + ((((uint64_t)par * world + src) * a.ll_src_rows + t) * s.xw + word) * 16;
+}
+__device__ __forceinline__ uint64_t ll_y_slot(const McbA2AStepArgs& a, const LLShape& s, int world, uint32_t par, int dst,
+                                              int t, int word) {
+  return a.ll_y_off + ((((uint64_t)par * world + dst) * a.ll_src_rows + t) * s.yw + word) * 16;
+}
+
+// Send one 8-byte word of token t's row to every destination in the mask.
+__device__ __forceinline__ void ll_send_x(const McbCtx& c, const McbA2AStepArgs& a, const LLShape& s, const DestMask& m,
+                                          uint32_t par, int t, int word, uint2 d, uint32_t flag) {
+  const uint4 pkt = ll_pack(d, flag);
+#pragma unroll 1
+  for (int wi = 0; wi < 3; ++wi) {
+    uint32_t bits = m.w[wi];
+    while (bits) {
+      const int dst = wi * 32 + __ffs(bits) - 1;
+      bits &= bits - 1;
+      st_v4(c.heap_peer[dst] + ll_x_slot(a, s, c.world, par, c.rank, t, word), pkt);
+    }
+  }
+}
+
+// Source side of a layer: header to every rank, row / scales / metadata to the routed destinations.  One warp.
+__device__ __forceinline__ void ll_dispatch_token(const McbCtx& c, const McbA2AStepArgs& a, const LLShape& s, int t,
+                                                  int epr, uint32_t par, uint32_t flag, int lane) {
+  const DestMask m = dest_mask(c, a, t, epr, lane);
+  for (int p = lane; p < c.world; p += 32) {
+    const uint32_t routed = (m.w[p >> 5] >> (p & 31)) & 1u;
+    st_v4(c.heap_peer[p] + ll_x_slot(a, s, c.world, par, c.rank, t, 0), ll_pack(make_uint2(routed, (uint32_t)t), flag));
+  }
+  const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.x) + (uint64_t)t * a.hidden * 2;
+  if (!a.fp8) {
+    for (int j = lane; j < s.xdata; j += 32) ll_send_x(c, a, s, m, par, t, 1 + j, ld_v2(xrow + (uint64_t)j * 8), flag);
+  } else {
+    const int row_packs = a.hidden / 8;
+    for (int p0 = 0; p0 < row_packs; p0 += 32) {      // row_packs is a multiple of 32 (hidden % 256 == 0)
+      const int p = p0 + lane;
+      const uint4 v = ld_v4(xrow + (uint64_t)p * 16);
+      float amax = pack_absmax(v);                     // 16 lanes hold one 128-value block
+#pragma unroll
+      for (int sh = 8; sh >= 1; sh >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
+      const float scale = e4m3_scale(amax);
+      ll_send_x(c, a, s, m, par, t, 1 + p, quant_pack_e4m3(v, scale), flag);
+      // lanes 0-15 hold block p0 / 16, lanes 16-31 the next one: one word carries both scales
+      const float other = __shfl_sync(0xffffffffu, scale, 16);
+      if (lane == 0)
+        ll_send_x(c, a, s, m, par, t, 1 + s.xdata + (p0 >> 5), make_uint2(__float_as_uint(scale), __float_as_uint(other)), flag);
+    }
+  }
+  // metadata row: chunk 0 = {stamp, token, id 0, weight 0}, chunk j = {id 2j-1, weight 2j-1, id 2j, weight 2j}
+  for (int j = lane; j < s.meta / 2; j += 32) {
+    const int k0 = j == 0 ? 0 : 2 * j - 1, k1 = 2 * j;
+    const long long tb = (long long)t * a.topk;
+    const uint32_t id0 = k0 < a.topk ? (uint32_t)a.topk_idx[tb + k0] : 0xffffffffu;
+    const uint32_t w0 = k0 < a.topk ? __float_as_uint(a.topk_w ? a.topk_w[tb + k0] : 1.0f) : 0u;
+    uint2 lo, hi;
+    if (j == 0) {
+      lo = make_uint2(flag, (uint32_t)t);
+      hi = make_uint2(id0, w0);
+    } else {
+      const uint32_t id1 = k1 < a.topk ? (uint32_t)a.topk_idx[tb + k1] : 0xffffffffu;
+      const uint32_t w1 = k1 < a.topk ? __float_as_uint(a.topk_w ? a.topk_w[tb + k1] : 1.0f) : 0u;
+      lo = make_uint2(id0, w0);
+      hi = make_uint2(id1, w1);
+    }
+    ll_send_x(c, a, s, m, par, t, 1 + s.xdata + s.scales + 2 * j, lo, flag);
+    ll_send_x(c, a, s, m, par, t, 1 + s.xdata + s.scales + 2 * j + 1, hi, flag);
+  }
+}
+
+// Destination side: wait for the header of (source, token); if the token is routed here, unpack its row
+// into the ordinary receive buffers and send the expert output (the row itself for the identity expert
+// in bf16, the y buffer otherwise) back to the source.  One warp.
+__device__ __forceinline__ void ll_serve_token(const McbCtx& c, const McbA2AStepArgs& a, const LLShape& s, int src, int t,
+                                               uint32_t par, uint32_t flag, int lane) {
+  uint32_t routed = 0;
+  if (lane == 0) routed = ll_wait(c, c.heap_local + ll_x_slot(a, s, c.world, par, src, t, 0), flag, MCB_SITE_A2A_STEP).x;
+  routed = __shfl_sync(0xffffffffu, routed, 0);
+  if (!routed) return;
+  const uint64_t row = (uint64_t)src * a.cap + t;
+  const uint64_t xrow_bytes = a.fp8 ? (uint64_t)a.hidden : (uint64_t)a.hidden * 2;
+  uint8_t* rx = c.heap_local + a.recv_x_off + (uint64_t)par * a.x_par_stride + row * xrow_bytes;
+  uint8_t* rs = c.heap_local + a.recv_scale_off + (uint64_t)par * a.scale_par_stride + row * (uint64_t)(a.hidden / 128) * 4;
+  uint8_t* rm = c.heap_local + a.recv_meta_off + (uint64_t)par * a.meta_par_stride + row * a.meta_row_bytes;
+  const uint8_t* yrow = c.heap_local + a.y_off + (uint64_t)par * a.y_par_stride + row * (uint64_t)a.hidden * 2;
+  const int body = s.xdata + s.scales + s.meta;
+  const bool echo = !a.fp8 && a.y_off == a.recv_x_off;     // identity expert on bf16 rows: the row is its own output
+  // poll 4 packets per lane at a time, wait only for those not there yet
+  for (int j0 = lane; j0 < body; j0 += 128) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u * 32;
+      if (j < body) v[u] = ld_v4_volatile(c.heap_local + ll_x_slot(a, s, c.world, par, src, t, 1 + j));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u * 32;
+      if (j >= body) continue;
+      uint2 d = make_uint2(v[u].x, v[u].z);
+      if (v[u].y != flag || v[u].w != flag)
+        d = ll_wait(c, c.heap_local + ll_x_slot(a, s, c.world, par, src, t, 1 + j), flag, MCB_SITE_A2A_STEP);
+      if (j < s.xdata) {
+        st_v2(rx + (uint64_t)j * 8, d);
+        if (echo) st_v4(c.heap_peer[src] + ll_y_slot(a, s, c.world, par, c.rank, t, j), ll_pack(d, flag));
+      } else if (j < s.xdata + s.scales) {
+        st_v2(rs + (uint64_t)(j - s.xdata) * 8, d);
+      } else {
+        st_v2(rm + (uint64_t)(j - s.xdata - s.scales) * 8, d);
+      }
+    }
+  }
+  if (!echo)     // the expert output is a bf16 row of its own
+    for (int j = lane; j < s.yw; j += 32)
+      st_v4(c.heap_peer[src] + ll_y_slot(a, s, c.world, par, c.rank, t, j), ll_pack(ld_v2(yrow + (uint64_t)j * 8), flag));
+}
+
+// Source side again: sum the expert outputs of every destination as their packets arrive.  One warp.
+__device__ __forceinline__ void ll_combine_token(const McbCtx& c, const McbA2AStepArgs& a, const LLShape& s, int t,
+                                                 int epr, uint32_t par, uint32_t flag, int lane) {
+  const DestMask m = dest_mask(c, a, t, epr, lane);
+  uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + (uint64_t)t * a.hidden * 2;
+  for (int j0 = lane; j0 < s.yw; j0 += 128) {
+    float acc[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
+#pragma unroll 1
+    for (int wi = 0; wi < 3; ++wi) {
+      uint32_t bits = m.w[wi];
+      while (bits) {
+        const int d = wi * 32 + __ffs(bits) - 1;
+        bits &= bits - 1;
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u * 32;
+          if (j < s.yw) v[u] = ld_v4_volatile(c.heap_local + ll_y_slot(a, s, c.world, par, d, t, j));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = j0 + u * 32;
+          if (j >= s.yw) continue;
+          uint2 w = make_uint2(v[u].x, v[u].z);
+          if (v[u].y != flag || v[u].w != flag)
+            w = ll_wait(c, c.heap_local + ll_y_slot(a, s, c.world, par, d, t, j), flag, MCB_SITE_A2A_STEP);
+          acc[u][0] += bf16_lo(w.x); acc[u][1] += bf16_hi(w.x);
+          acc[u][2] += bf16_lo(w.y); acc[u][3] += bf16_hi(w.y);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u * 32;
+      if (j < s.yw)
+        st_v2(orow + (uint64_t)j * 8, make_uint2(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3])));
+    }
+  }
 }
 
 template <bool EMU>
@@ -71,6 +248,44 @@ __global__ void __launch_bounds__(512) a2a_step_kernel(const __grid_constant__ M
     a.step_meta[5] = L > 0 ? (int)((layer_base + (uint32_t)L - 1u) & 1u) : 0;
     a.step_meta[7] = (int)(layer_base + (uint32_t)L);     // stamp of the last layer's rows
   }
+  const int valid = s_prefix[W];
+  LLShape shp;
+  shp.xdata = a.fp8 ? a.hidden / 8 : a.hidden / 4;
+  shp.scales = a.fp8 ? a.hidden / 256 : 0;
+  shp.meta = (int)(a.meta_row_bytes >> 3);
+  shp.xw = 1 + shp.xdata + shp.scales + shp.meta;
+  shp.yw = a.hidden / 4;
+  const bool ll = W > 1 && a.ll_rows > 0 && valid > 0 && valid <= a.ll_rows && (!a.fp8 || a.hidden % 256 == 0);
+  if (bid == 0 && tid == 0) a.step_meta[6] = ll ? 1 : 0;
+  if (ll) {
+    // ---- packet mode: global token g belongs to warp slot g % (blocks * warps) on every rank ----
+    int nb = (valid + nwarps - 1) / nwarps;
+    nb = nb > (int)gridDim.x ? (int)gridDim.x : nb;
+    if (bid < nb) {
+      const int slots = nb * nwarps, slot = bid * nwarps + warp;
+      const int epr_ll = a.num_experts / W;
+      const int offset = s_prefix[c.rank];
+      const uint32_t cb = *epoch_ptr(c, MCB_SITE_A2A_STEP_CREDIT, bid);
+      for (int l = 0; l < L; ++l) {
+        const uint32_t par = (layer_base + (uint32_t)l) & 1u;
+        const uint32_t flag = layer_base + (uint32_t)l + 1u;
+        // the staging areas of this parity were read last in layer l - 2
+        if (l >= 2) credit_wait(c, a.credit_off, cb + (uint32_t)l - 1u, MCB_SITE_A2A_STEP_CREDIT);
+        // first own token with (offset + t) % slots == slot
+        const int t0 = ((slot - offset) % slots + slots) % slots;
+        for (int t = t0; t < n; t += slots) ll_dispatch_token(c, a, shp, t, epr_ll, par, flag, lane);
+        for (int g = slot; g < valid; g += slots) {
+          int src = 0;
+          while (src + 1 < W && s_prefix[src + 1] <= g) ++src;
+          ll_serve_token(c, a, shp, src, g - s_prefix[src], par, flag, lane);
+        }
+        for (int t = t0; t < n; t += slots) ll_combine_token(c, a, shp, t, epr_ll, par, flag, lane);
+        __syncthreads();
+        credit_publish(c, a.credit_off, cb + (uint32_t)l + 1u);
+      }
+      if (tid == 0) *epoch_ptr(c, MCB_SITE_A2A_STEP_CREDIT, bid) = cb + (uint32_t)L;
+    }
+  }
   // One warp per token; as many blocks as the largest rank needs, the same on every rank.
   int nact = (ep_max + nwarps - 1) / nwarps;
   nact = nact > (int)gridDim.x ? (int)gridDim.x : nact;
@@ -83,7 +298,7 @@ __global__ void __launch_bounds__(512) a2a_step_kernel(const __grid_constant__ M
   const uint8_t* x = reinterpret_cast<const uint8_t*>(a.x);
   uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
 
-  if (bid < nact) {
+  if (!ll && bid < nact) {
     uint32_t ep = *epoch_ptr(c, MCB_SITE_A2A_STEP, bid);
     for (int l = 0; l < L; ++l) {
       const uint32_t par = (layer_base + (uint32_t)l) & 1u;
@@ -248,6 +463,7 @@ static int check_a2a_step(const McbCtx* ctx, const McbA2AStepArgs* a, int grid, 
   if (a->hidden < 8 || a->hidden % 8 || (a->fp8 && a->hidden % 128) || a->topk < 1 || a->cap < 1 || a->num_layers < 0) return 1;
   if (ctx->world < 1 || a->num_experts % ctx->world) return 1;
   if ((a->meta_row_bytes & 15u) || a->meta_row_bytes < 8u + 8u * (uint32_t)a->topk) return 1;
+  if (a->ll_rows > 0 && (!a->ll_x_off || !a->ll_y_off || !a->credit_off || a->ll_src_rows < 1 || a->hidden % 4)) return 1;
   return 0;
 }
 

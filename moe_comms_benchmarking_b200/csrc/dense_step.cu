@@ -80,40 +80,6 @@ __device__ __forceinline__ void check_fail(const McbDenseStepArgs& a) {
   if (a.check_errors) atomicAdd(a.check_errors, 1u);
 }
 
-// Credits of the packet mode: credit[block][source rank] = number of packet layers whose packets the
-// source's block has finished reading (monotonic; written by that rank only, on every rank).
-__device__ __forceinline__ uint64_t credit_off(const McbDenseStepArgs& a, int block, int rank) {
-  return a.credit_off + ((uint64_t)block * MCB_MAX_RANKS + (uint64_t)rank) * 4;
-}
-// All threads: the first `world` threads publish (or wait for) one word each.
-__device__ __forceinline__ void credit_publish(const McbCtx& c, const McbDenseStepArgs& a, uint32_t value) {
-  const uint64_t off = credit_off(a, blockIdx.x, c.rank);
-  if (c.transport == MCB_TRANSPORT_MULTIMEM) {
-    if (threadIdx.x == 0) mm_st_b32(c.heap_mc + off, value);
-  } else {
-    for (int p = threadIdx.x; p < c.world; p += blockDim.x) st_relaxed_sys(c.heap_peer[p] + off, value);
-  }
-}
-__device__ __forceinline__ void credit_wait(const McbCtx& c, const McbDenseStepArgs& a, uint32_t target) {
-  for (int p = threadIdx.x; p < c.world; p += blockDim.x) {
-    const uint8_t* w = c.heap_local + credit_off(a, blockIdx.x, p);
-    uint32_t v = ld_relaxed_sys(w);
-    if ((int32_t)(v - target) >= 0) continue;
-    const uint64_t t0 = globaltimer_ns();
-    for (;;) {
-#pragma unroll 1
-      for (int i = 0; i < 64 && (int32_t)(v - target) < 0; ++i) v = ld_relaxed_sys(w);
-      if ((int32_t)(v - target) >= 0) break;
-      const bool poisoned = *reinterpret_cast<volatile uint32_t*>(c.status) != 0u;
-      if (poisoned || globaltimer_ns() - t0 > c.timeout_ns) {
-        report_error(c, MCB_ERR_TIMEOUT, MCB_SITE_STEP_CREDIT, blockIdx.x, v, target);
-        break;
-      }
-    }
-  }
-  __syncthreads();
-}
-
 // Packet all-gather of one layer.  Slot i = (global row) * wpr + word is sent by thread
 // (i mod nthreads) of the row's owner and read by the same thread index on every rank.
 // The 8 payload bytes of word j of gathered tensor t of local row `row` when the hidden rows are
@@ -394,14 +360,14 @@ __global__ void __launch_bounds__(512) dense_step_kernel(const __grid_constant__
         const uint32_t par = (layer_base + (uint32_t)l) & 1u;
         // The staging area of this parity was read last in layer l - 2 (every rank has left the
         // previous step: nothing to wait for in the first two layers).
-        if (l >= 2) credit_wait(c, a, cb + (uint32_t)l - 1u);
+        if (l >= 2) credit_wait(c, a.credit_off, cb + (uint32_t)l - 1u, MCB_SITE_STEP_CREDIT);
         if (CHECK && a.delay_ns && (l + c.rank) % (a.delay_every < 1 ? 1 : a.delay_every) == 0)
           __nanosleep(a.delay_ns > 1000000u ? 1000000u : a.delay_ns);
         step_agv_ll<CHECK, FP8>(c, a, shp, n, offset, valid, flag, par, layer_base + (uint32_t)l, gtid, nthreads);
         __syncthreads();      // the block holds all its gathered words before it starts the combine
         step_rsv_ll(c, a, s_prefix, n, ep_max, flag, gtid, nthreads);
         __syncthreads();
-        credit_publish(c, a, cb + (uint32_t)l + 1u);
+        credit_publish(c, a.credit_off, cb + (uint32_t)l + 1u);
       }
       if (tid == 0) *epoch_ptr(c, MCB_SITE_STEP_CREDIT, bid) = cb + (uint32_t)L;
     }

@@ -41,6 +41,7 @@
 #define MCB_SITE_STEP 18          // block-matched barrier of each layer of a persistent decode step
 #define MCB_SITE_A2A_STEP_META 20 // count exchange at the start of a persistent all-to-all step (slot 0)
 #define MCB_SITE_A2A_STEP 21      // block-matched barrier of each layer of a persistent all-to-all step
+#define MCB_SITE_A2A_STEP_CREDIT 22  // per-block count of packet-mode layers of the all-to-all step (epochs only)
 #define MCB_SITE_STEP_CREDIT 19   // per-block count of packet-mode layers (epochs only; the credit words are
                                   // in a heap region of their own, McbDenseStepArgs::credit_off)
 
@@ -223,10 +224,19 @@ typedef struct {
   int32_t cap;
   int32_t fp8;
   int32_t num_layers;
-  int32_t reserved0;
-  int32_t* step_meta;          // local int32[8]: valid, offset, max, -, step number, parity of the last layer, -, stamp of the last layer
+  int32_t ll_rows;             // packet mode when the step holds at most this many tokens over all ranks (0 = never)
+  int32_t* step_meta;          // local int32[8]: valid, offset, max, -, step number, parity of the last layer, mode, stamp of the last layer
   uint64_t counts_off;         // heap: int32 counts[2][MCB_MAX_RANKS] of this kernel
   uint32_t* state;             // local uint32[MCB_STEP_STATE_WORDS] (step_seq, layer_base, -, finished)
+  // Packet mode: rows travel as 16-byte {data, flag, data, flag} packets.  Dispatch staging on the
+  // destination: [2][world][ll_src_rows][1 + row words + scale words + metadata words] packets (word 0 is
+  // a header {routed here?, token} that EVERY rank receives for every token, so a destination knows what
+  // to wait for); combine staging on the source: [2][world][ll_src_rows][hidden / 4] packets.
+  uint64_t ll_x_off;
+  uint64_t ll_y_off;
+  uint64_t credit_off;         // heap: uint32 credit[grid][MCB_MAX_RANKS] (zero at start)
+  int32_t ll_src_rows;         // min(cap, ll_rows)
+  int32_t reserved1;
 } McbA2AStepArgs;
 
 // All-to-all-V combine: out[t,:] = sum over destination ranks d of y_d[rank][slot_map[t][d],:].

@@ -56,4 +56,39 @@ __device__ __forceinline__ int step_count_exchange(const McbCtx& c, int site, ui
   return n;
 }
 
+// Credits of the packet modes: credit[block][source rank] = number of packet layers whose packets the
+// source's block has finished reading (monotonic; written by that rank only, on every rank).  A sum over
+// ranks could not tell a slow rank from fast ones that ran ahead, hence one word per source.
+__device__ __forceinline__ uint64_t credit_word_off(uint64_t credit_off, int block, int rank) {
+  return credit_off + ((uint64_t)block * MCB_MAX_RANKS + (uint64_t)rank) * 4;
+}
+// All threads: the first `world` threads publish (or wait for) one word each.
+__device__ __forceinline__ void credit_publish(const McbCtx& c, uint64_t credit_off, uint32_t value) {
+  const uint64_t off = credit_word_off(credit_off, blockIdx.x, c.rank);
+  if (c.transport == MCB_TRANSPORT_MULTIMEM) {
+    if (threadIdx.x == 0) mm_st_b32(c.heap_mc + off, value);
+  } else {
+    for (int p = threadIdx.x; p < c.world; p += blockDim.x) st_relaxed_sys(c.heap_peer[p] + off, value);
+  }
+}
+__device__ __forceinline__ void credit_wait(const McbCtx& c, uint64_t credit_off, uint32_t target, int site) {
+  for (int p = threadIdx.x; p < c.world; p += blockDim.x) {
+    const uint8_t* w = c.heap_local + credit_word_off(credit_off, blockIdx.x, p);
+    uint32_t v = ld_relaxed_sys(w);
+    if ((int32_t)(v - target) >= 0) continue;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+      for (int i = 0; i < 64 && (int32_t)(v - target) < 0; ++i) v = ld_relaxed_sys(w);
+      if ((int32_t)(v - target) >= 0) break;
+      const bool poisoned = *reinterpret_cast<volatile uint32_t*>(c.status) != 0u;
+      if (poisoned || globaltimer_ns() - t0 > c.timeout_ns) {
+        report_error(c, MCB_ERR_TIMEOUT, (uint32_t)site, blockIdx.x, v, target);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+}
+
 }  // namespace mcb

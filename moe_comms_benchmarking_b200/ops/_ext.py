@@ -28,7 +28,7 @@ SITE_FUSED_FC1, SITE_FUSED_FC2, SITE_LAYER, SITE_TEST = 9, 10, 11, 15
 SITE_AGV_LL, SITE_RSV_LL = 12, 13
 SITE_A2A_GO, SITE_FC1_FUSED = 14, 16
 SITE_STEP_META, SITE_STEP, SITE_STEP_CREDIT = 17, 18, 19
-SITE_A2A_STEP_META, SITE_A2A_STEP = 20, 21
+SITE_A2A_STEP_META, SITE_A2A_STEP, SITE_A2A_STEP_CREDIT = 20, 21, 22
 LL_SITES = (SITE_AGV_LL, SITE_RSV_LL, SITE_FC1_FUSED)
 STEP_STATE_WORDS = 16
 STATE_STEP_SEQ, STATE_LAYER_BASE, STATE_LL_BASE, STATE_FINISHED, STATE_GATE0 = 0, 1, 2, 3, 4
@@ -101,8 +101,9 @@ class McbA2AStepArgs(C.Structure):
         ("recv_x_off", _u64), ("recv_scale_off", _u64), ("recv_meta_off", _u64), ("y_off", _u64),
         ("x_par_stride", _u64), ("scale_par_stride", _u64), ("meta_par_stride", _u64), ("y_par_stride", _u64),
         ("meta_row_bytes", _u32), ("hidden", _i32), ("topk", _i32), ("num_experts", _i32), ("cap", _i32),
-        ("fp8", _i32), ("num_layers", _i32), ("reserved0", _i32),
+        ("fp8", _i32), ("num_layers", _i32), ("ll_rows", _i32),
         ("step_meta", _vp), ("counts_off", _u64), ("state", _vp),
+        ("ll_x_off", _u64), ("ll_y_off", _u64), ("credit_off", _u64), ("ll_src_rows", _i32), ("reserved1", _i32),
     ]
 
 

@@ -117,16 +117,44 @@ def a2a_meta_row_bytes(topk: int) -> int:
     return (8 + 8 * topk + 15) // 16 * 16
 
 
+def a2a_ll_words(hidden: int, topk: int, fp8: bool):
+    """8-byte words per token of the packet-mode staging areas: (dispatch incl. the header word, combine)."""
+    xdata = hidden // 8 if fp8 else hidden // 4
+    scales = hidden // 256 if fp8 else 0
+    return 1 + xdata + scales + a2a_meta_row_bytes(topk) // 8, hidden // 4
+
+
+def a2a_ll_specs(world: int, cap: int, hidden: int, topk: int, fp8: bool, ll_rows: int):
+    """Heap regions of packet mode: dispatch staging, combine staging, per-(block, source) credit words."""
+    if ll_rows <= 0 or world == 1:
+        return []
+    src_rows = min(cap, ll_rows)
+    xw, yw = a2a_ll_words(hidden, topk, fp8)
+    return [([2 * world * src_rows * xw * 16], torch.uint8), ([2 * world * src_rows * yw * 16], torch.uint8),
+            ([_ext.MAX_BLOCKS * _ext.MAX_RANKS * 4], torch.uint8)]
+
+
 class A2AStepBuffers:
     """Heap buffers of the persistent all-to-all step kernel, double buffered by layer parity:
     ``recv_x [2, world, cap, hidden]`` (bf16, or e4m3 bytes with ``recv_scale [2, world, cap, hidden/128]``),
     ``recv_meta [2, world, cap, meta_row_bytes]`` and the expert outputs ``y`` (the received rows themselves
-    for the identity expert in bf16).  A token's slot on every destination is its own index."""
+    for the identity expert in bf16).  A token's slot on every destination is its own index.  With
+    ``ll_rows > 0`` the packet-mode staging areas and credit words are allocated too (e4m3 packet mode needs
+    ``hidden % 256 == 0``; otherwise the kernel stays on the barrier path)."""
 
-    def __init__(self, heap: SymmetricHeap, cap: int, hidden: int, topk: int, fp8: bool, prefix: str = "a2as"):
+    def __init__(self, heap: SymmetricHeap, cap: int, hidden: int, topk: int, fp8: bool, prefix: str = "a2as",
+                 ll_rows: int = 0):
         w = heap.world
         self.cap, self.hidden, self.topk, self.fp8 = cap, hidden, topk, fp8
         self.meta_row_bytes = a2a_meta_row_bytes(topk)
+        self.ll_rows = int(ll_rows) if w > 1 and hidden % 4 == 0 else 0
+        self.ll_x = self.ll_y = self.credits = None
+        if self.ll_rows > 0:
+            sx, sy, sc = a2a_ll_specs(w, cap, hidden, topk, fp8, self.ll_rows)
+            self.ll_x = heap.alloc(f"{prefix}_ll_x", sx[0], torch.uint8)
+            self.ll_y = heap.alloc(f"{prefix}_ll_y", sy[0], torch.uint8)
+            self.credits = heap.alloc(f"{prefix}_credit", sc[0], torch.uint8)
+            self.credits.tensor.zero_()
         if hidden % 8 or (fp8 and hidden % 128):
             raise ValueError("hidden must be a multiple of 8 (128 with fp8 dispatch)")
         if fp8:
@@ -140,8 +168,9 @@ class A2AStepBuffers:
         self.recv_meta = heap.alloc(f"{prefix}_recv_meta", [2, w, cap, self.meta_row_bytes], torch.uint8)
 
     @staticmethod
-    def specs(world: int, cap: int, hidden: int, topk: int, fp8: bool):
+    def specs(world: int, cap: int, hidden: int, topk: int, fp8: bool, ll_rows: int = 0):
         s = [([2, world, cap, a2a_meta_row_bytes(topk)], torch.uint8)]
+        s += a2a_ll_specs(world, cap, hidden, topk, fp8, ll_rows if hidden % 4 == 0 else 0)
         if fp8:
             s += [([2, world, cap, hidden], torch.uint8), ([2, world, cap, hidden // 128], torch.float32),
                   ([2, world, cap, hidden], torch.bfloat16)]
@@ -195,6 +224,11 @@ class A2AStepPlan:
         a.meta_row_bytes, a.hidden, a.topk, a.num_experts = bufs.meta_row_bytes, bufs.hidden, bufs.topk, int(num_experts)
         a.cap, a.fp8, a.num_layers = bufs.cap, int(bufs.fp8), int(num_layers)
         a.step_meta, a.counts_off, a.state = step_meta.data_ptr(), heap.a2a_counts_off, state.data_ptr()
+        if bufs.ll_rows > 0:
+            for name in ("ll_x", "ll_y", "credits"):
+                _check_heap_tensor(heap, getattr(bufs, name), name)
+            a.ll_rows, a.ll_src_rows = bufs.ll_rows, min(bufs.cap, bufs.ll_rows)
+            a.ll_x_off, a.ll_y_off, a.credit_off = bufs.ll_x.offset, bufs.ll_y.offset, bufs.credits.offset
         self.args = a
 
     def launch(self, pdl: bool = False, stream=None):

@@ -23,10 +23,11 @@ NUM_SMS = 148
 BLOCK_M = 128
 
 
-def _swizzle_index(device) -> torch.Tensor:
-    """index[r, c'] = c' ^ (r % 8): which 16-byte chunk of row r sits at position c' of the swizzled row."""
-    r = torch.arange(128, device=device).view(128, 1) % 8
-    return torch.arange(8, device=device).view(1, 8) ^ r
+def _swizzle(t: torch.Tensor) -> torch.Tensor:
+    """``t[..., 8 (row % 8), 8 (16-byte chunk), 8 values]`` -> chunk c of row r moved to position c ^ r (its own inverse)."""
+    r = torch.arange(8, device=t.device).view(8, 1)
+    c = torch.arange(8, device=t.device).view(1, 8) ^ r
+    return t[..., r, c, :]
 
 
 def pack_weight_tiles(w: torch.Tensor) -> torch.Tensor:
@@ -36,17 +37,15 @@ def pack_weight_tiles(w: torch.Tensor) -> torch.Tensor:
     E, R, K = w.shape
     if R % 128 or K % 64:
         raise ValueError("rows must be a multiple of 128 and columns a multiple of 64")
-    t = w.view(E, R // 128, 128, K // 64, 8, 8).permute(0, 1, 3, 2, 4, 5)      # [E, RB, KB, 128, chunk, 8]
-    idx = _swizzle_index(w.device).view(1, 1, 1, 128, 8, 1).expand(E, R // 128, K // 64, 128, 8, 8)
-    return torch.gather(t, 4, idx).contiguous().view(E, R // 128, K // 64, 128, 64)
+    t = w.view(E, R // 128, 16, 8, K // 64, 8, 8).permute(0, 1, 4, 2, 3, 5, 6)      # [E, RB, KB, 16, row % 8, chunk, 8]
+    return _swizzle(t).contiguous().view(E, R // 128, K // 64, 128, 64)
 
 
 def unpack_weight_tiles(p: torch.Tensor) -> torch.Tensor:
-    """Inverse of ``pack_weight_tiles`` (the swizzle is its own inverse)."""
+    """Inverse of ``pack_weight_tiles``."""
     E, RB, KB = p.shape[:3]
-    t = p.view(E, RB, KB, 128, 8, 8)
-    idx = _swizzle_index(p.device).view(1, 1, 1, 128, 8, 1).expand(E, RB, KB, 128, 8, 8)
-    return torch.gather(t, 4, idx).permute(0, 1, 3, 2, 4, 5).contiguous().view(E, RB * 128, KB * 64)
+    t = _swizzle(p.view(E, RB, KB, 16, 8, 8, 8))                                    # [E, RB, KB, 16, row % 8, chunk, 8]
+    return t.permute(0, 1, 3, 4, 2, 5, 6).contiguous().view(E, RB * 128, KB * 64)
 
 
 class ExpertWeights:

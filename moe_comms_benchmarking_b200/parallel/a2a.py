@@ -20,12 +20,23 @@ from .base import Dispatcher
 from .symm_heap import SymmetricHeap, required_bytes
 
 
+def resolve_a2a_ll_rows(cfg: Config, ll_rows: int) -> int:
+    """Largest step (tokens over all ranks) the packet mode of the persistent kernel serves; 0 = off, which is
+    also the default (-1): on two GPUs the barrier path measured faster at every step size (a layer is two
+    one-way trips either way, and packets double the bytes on the wire)."""
+    if cfg.ep_size == 1:
+        return 0
+    if ll_rows < 0:
+        ll_rows = 0
+    return min(int(ll_rows), max(cfg.global_cap, 1))
+
+
 class A2ADispatcher(Dispatcher):
     name = "a2a"
 
     def __init__(self, cfg: Config, group, heap: SymmetricHeap | None = None, num_sms: int = DEFAULT_GRID,
                  threads: int = DEFAULT_THREADS, pdl: bool = True, fp8_dispatch: bool = False,
-                 transport: str = "auto", persistent: bool = True, device=None):
+                 transport: str = "auto", persistent: bool = True, ll_rows: int = -1, device=None):
         super().__init__(cfg, group, device)
         self.heap = heap
         self._own_heap = heap is None
@@ -37,24 +48,29 @@ class A2ADispatcher(Dispatcher):
         # persistent: a whole decode step is ONE kernel (token-indexed slots, one barrier per layer);
         # otherwise 2 x layers launches of the dispatch / combine kernels with compacted slots and counts.
         self.persistent = bool(persistent)
+        # packet mode of the persistent kernel serves steps of at most ll_rows tokens over all ranks
+        self.ll_rows = resolve_a2a_ll_rows(cfg, ll_rows) if self.persistent else 0
         self.kernel_launches_per_step = lambda nl: 1 if self.persistent else 2 * nl
         self._step_plans = {}
 
     @staticmethod
-    def heap_specs(cfg: Config, fp8: bool = False):
+    def heap_specs(cfg: Config, fp8: bool = False, ll_rows: int = -1):
         cap = max(cfg.per_rank_cap, 1)
         return (A2ABuffers.specs(cfg.ep_size, cap, cfg.hidden, cfg.topk, fp8)
-                + A2AStepBuffers.specs(cfg.ep_size, cap, cfg.hidden, cfg.topk, fp8))
+                + A2AStepBuffers.specs(cfg.ep_size, cap, cfg.hidden, cfg.topk, fp8, resolve_a2a_ll_rows(cfg, ll_rows)))
 
     def build(self):
         cfg, dev = self.cfg, self.device
         cap, H, K = max(cfg.per_rank_cap, 1), cfg.hidden, cfg.topk
         self.cap = cap
         if self.heap is None:
-            self.heap = SymmetricHeap(self.group, required_bytes(self.heap_specs(cfg, self.fp8)), dev,
+            self.heap = SymmetricHeap(self.group, required_bytes(self.heap_specs(cfg, self.fp8, self.ll_rows)), dev,
                                       transport=self.transport)
         self.bufs = A2ABuffers(self.heap, cap, H, K, self.fp8, prefix="a2a8" if self.fp8 else "a2a")
-        self.step_bufs = A2AStepBuffers(self.heap, cap, H, K, self.fp8, prefix="a2as8" if self.fp8 else "a2as")
+        self.step_bufs = A2AStepBuffers(self.heap, cap, H, K, self.fp8, prefix="a2as8" if self.fp8 else "a2as",
+                                        ll_rows=self.ll_rows)
+        if self.step_bufs.credits is not None:        # the per-block credit counts restart with the epochs
+            self.heap.register_reset_hook(self.step_bufs.credits.tensor.zero_)
         self.step_metadata = torch.zeros(8, dtype=torch.int32, device=dev)
         self.step_state = torch.zeros(_ext.STEP_STATE_WORDS, dtype=torch.int32, device=dev)
         self.heap.register_reset_hook(self.step_state.zero_)
@@ -223,10 +239,12 @@ class A2ADispatcher(Dispatcher):
         tol = 0.08 if self.fp8 else 0.05
         results = []
         if self.persistent:
-            for B in (w * 2, 1):
+            # small steps run the packet mode (when enabled), the last one the barrier path
+            for B in (w * 2, 1, self.ll_rows + w):
                 if max(self._validation_counts(B)) <= self.cap:
                     ok, detail = self._validate_step_kernel(B)
-                    results.append((f"{self.name} step kernel       B={B:<4d}", bool(ok), detail))
+                    mode = "packets" if int(self.step_metadata[6]) else "barrier"
+                    results.append((f"{self.name} step kernel       B={B:<4d}", bool(ok), f"[{mode}] {detail}"))
         for B in (w * 2, 1):
             counts = self._validation_counts(B)
             if max(counts) > self.cap:

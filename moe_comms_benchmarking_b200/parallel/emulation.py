@@ -293,10 +293,17 @@ class EmuWorld:
                                                       self.world, grid, threads, self._stream()), "emu a2a combine")
         torch.cuda.synchronize()
 
-    def a2a_step_buffers(self, cap, hidden, topk, fp8):
-        from ..ops.a2a import a2a_meta_row_bytes
+    def a2a_step_buffers(self, cap, hidden, topk, fp8, ll_rows=0):
+        from ..ops.a2a import a2a_ll_specs, a2a_meta_row_bytes
         w = self.world
-        b = {"cap": cap, "hidden": hidden, "topk": topk, "fp8": fp8, "meta_row_bytes": a2a_meta_row_bytes(topk)}
+        b = {"cap": cap, "hidden": hidden, "topk": topk, "fp8": fp8, "meta_row_bytes": a2a_meta_row_bytes(topk),
+             "ll_rows": ll_rows if w > 1 else 0}
+        if b["ll_rows"] > 0:
+            sx, sy, sc = a2a_ll_specs(w, cap, hidden, topk, fp8, ll_rows)
+            b["ll_x"], b["ll_y"], b["credits"] = (self.alloc(sx[0], torch.uint8), self.alloc(sy[0], torch.uint8),
+                                                  self.alloc(sc[0], torch.uint8))
+            for t in b["credits"]:
+                t.tensor.zero_()
         if fp8:
             b["recv_x"] = self.alloc([2, w, cap, hidden], torch.uint8)
             b["recv_scale"] = self.alloc([2, w, cap, hidden // 128], torch.float32)
@@ -323,6 +330,9 @@ class EmuWorld:
             a.meta_row_bytes, a.hidden, a.topk, a.num_experts = b["meta_row_bytes"], b["hidden"], b["topk"], num_experts
             a.cap, a.fp8, a.num_layers = b["cap"], int(b["fp8"]), num_layers
             a.step_meta, a.counts_off, a.state = step_metas[r].data_ptr(), self.a2a_counts_off, self.a2a_state[r].data_ptr()
+            if b.get("ll_rows", 0) > 0:
+                a.ll_rows, a.ll_src_rows = b["ll_rows"], min(b["cap"], b["ll_rows"])
+                a.ll_x_off, a.ll_y_off, a.credit_off = b["ll_x"][r].offset, b["ll_y"][r].offset, b["credits"][r].offset
             args.append(a)
         d = self.upload(args)
         _ext.check(_ext.require().mcb_emu_a2a_step(C.c_void_p(self.d_ctx.data_ptr()), C.c_void_p(d.data_ptr()),

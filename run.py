@@ -73,7 +73,7 @@ def parse_args(argv=None):
     p.add_argument("--expert", choices=["identity", "swiglu"], default="identity",
                    help="swiglu: real experts (dense/fused -> the fused expert path, nccl -> NCCL + library GEMMs)")
     p.add_argument("--no-persistent", action="store_true",
-                   help="dense: one kernel per operation (1 + 2 x layers launches) instead of one per decode step")
+                   help="dense / a2a: one kernel per operation (1 + 2 x layers / 2 x layers launches) instead of one per decode step")
     p.add_argument("--groups", type=int, default=1,
                    help="dense: pipeline groups of the persistent step kernel (1 = none)")
     p.add_argument("--no-layer-kernel", action="store_true",
@@ -83,6 +83,9 @@ def parse_args(argv=None):
     p.add_argument("--ll-rows", type=int, default=-1,
                    help="dense dispatcher: steps with at most this many tokens over all ranks use "
                         "low-latency flagged packets instead of barrier + multicast (0 = never, -1 = measured default)")
+    p.add_argument("--a2a-ll-rows", type=int, default=-1,
+                   help="all-to-all dispatcher: steps with at most this many tokens over all ranks run the packet mode "
+                        "of the persistent step kernel (0 = never, -1 = measured default)")
     p.add_argument("--no-pdl", action="store_true", help="disable programmatic dependent launch")
     p.add_argument("--coop-pdl", action="store_true",
                    help="fused: also allow programmatic dependent launch on the cooperative fused kernels")
@@ -132,14 +135,15 @@ def build_dispatchers(names, cfg, group, args, device, sms_list):
         if "dense" in names:
             specs += DenseDispatcher.heap_specs(cfg, ll_rows=args.ll_rows, fp8=fp8)
         if "a2a" in names:
-            specs += A2ADispatcher.heap_specs(cfg, fp8)
+            specs += A2ADispatcher.heap_specs(cfg, fp8, args.a2a_ll_rows)
         if "fused" in names:
             from moe_comms_benchmarking_b200.parallel.fused import FusedExpertDispatcher
             specs += FusedExpertDispatcher.heap_specs(cfg, ll_rows=args.ll_rows)
         heap = SymmetricHeap(group, required_bytes(specs), device, transport=args.transport)
     for n in names:
         if n == "a2a":
-            out.append(A2ADispatcher(cfg, group, heap, num_sms=sms_list[0], pdl=not args.no_pdl, fp8_dispatch=fp8))
+            out.append(A2ADispatcher(cfg, group, heap, num_sms=sms_list[0], pdl=not args.no_pdl, fp8_dispatch=fp8,
+                                     persistent=not args.no_persistent, ll_rows=args.a2a_ll_rows))
         elif n == "dense":
             out.append(DenseDispatcher(cfg, group, heap, num_sms=args.dense_num_sms, pdl=not args.no_pdl,
                                        ll_rows=args.ll_rows, persistent=not args.no_persistent, groups=args.groups,

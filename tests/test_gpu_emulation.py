@@ -202,28 +202,38 @@ def test_launch_numbers_do_not_depend_on_the_grid(lib):
     w.check_status()
 
 
+@pytest.mark.parametrize("ll_rows", [0, 20])
 @pytest.mark.parametrize("fp8", [False, True])
 @pytest.mark.parametrize("grid,threads", [(1, 64), (6, 256)])
-def test_a2a_step_kernel(lib, fp8, grid, threads):
+def test_a2a_step_kernel(lib, fp8, grid, threads, ll_rows):
     """The persistent all-to-all step (count exchange + every layer in one launch): token-indexed
-    slots, packed metadata rows with the layer's stamp, one barrier per layer; steps of 1-3 layers with
-    idle ranks; received rows / routing / stamps and the combined m * x against the oracle."""
+    slots, packed metadata rows with the layer's stamp, one barrier per layer; steps of 1-5 layers with
+    idle ranks; received rows / routing / stamps and the combined rows against the oracle.  With
+    ``ll_rows`` the small steps run in packet mode (flagged packets, credits, no barrier) and the step of 48
+    tokens on the barrier path, in the same sequence of launches."""
     W, E, K, H, cap = 4, 32, 6, 512, 12
     w = EmuWorld(W, 16 << 20, DEV)
-    b = w.a2a_step_buffers(cap, H, K, fp8)
+    b = w.a2a_step_buffers(cap, H, K, fp8, ll_rows=ll_rows)
     g = torch.Generator(device=DEV).manual_seed(29)
     metas = [torch.zeros(8, dtype=torch.int32, device=DEV) for _ in range(W)]
     outs = [torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV) for _ in range(W)]
     epr = E // W
-    for counts, layers in (([5, 0, 12, 3], 3), ([1, 0, 0, 0], 2), ([0, 0, 0, 0], 1), ([12, 12, 12, 12], 2), ([2, 7, 1, 4], 1)):
+    if fp8:
+        for r in range(W):
+            b["y"][r].tensor.copy_(torch.randn(2, W, cap, H, device=DEV, generator=g))
+    for counts, layers in (([5, 0, 12, 3], 5), ([1, 0, 0, 0], 2), ([0, 0, 0, 0], 1), ([12, 12, 12, 12], 2), ([2, 7, 1, 4], 1),
+                           ([3, 3, 3, 3], 4)):
         xs = [torch.randn(cap, H, device=DEV, generator=g).to(torch.bfloat16) for _ in range(W)]
         idxs = [torch.stack([torch.randperm(E, device=DEV, generator=g)[:K] for _ in range(cap)]) for _ in range(W)]
         ws = [torch.rand(cap, K, device=DEV, generator=g) for _ in range(W)]
         if fp8:
             xs[0][0, :128] = 0
+        for o in outs:
+            o.fill_(-7.0)
         w.a2a_step(b, xs, idxs, ws, outs, _scalars(counts), metas, E, layers, grid=grid, threads=threads)
         par, stamp = int(metas[0][5]), int(metas[0][7])
         assert metas[0][:3].tolist() == oracle.metadata(counts)[0]
+        assert int(metas[0][6]) == int(0 < sum(counts) <= ll_rows)
         for d in range(W):
             for s in range(W):
                 c = counts[s]
@@ -248,10 +258,18 @@ def test_a2a_step_kernel(lib, fp8, grid, threads):
                     assert ((back - want).abs() <= 0.0625 * want.abs() + 2e-3 * sc.repeat_interleave(128, dim=1)).all()
                 else:
                     assert torch.equal(b["recv_x"][d].tensor[par, s][sel], xs[s][sel])
-        if not fp8:         # identity expert: the combine reads the received rows
-            for r in range(W):
-                ref = oracle.roundtrip_identity(xs[r][:counts[r]], idxs[r][:counts[r]].cpu(), E, W)
-                assert torch.allclose(outs[r][:counts[r]].float().cpu(), ref, rtol=2e-2, atol=2e-2)
+        for r in range(W):
+            c = counts[r]
+            if not c:
+                continue
+            if not fp8:         # identity expert: the combine reads the received rows
+                ref = oracle.roundtrip_identity(xs[r][:c], idxs[r][:c].cpu(), E, W)
+            else:               # the sum of one expert-output row per distinct destination rank
+                ref = torch.zeros(c, H)
+                for d in range(W):
+                    here = ((idxs[r][:c] // epr) == d).any(dim=1).cpu()
+                    ref += b["y"][d].tensor[par, r, :c].float().cpu() * here[:, None]
+            assert torch.allclose(outs[r][:c].float().cpu(), ref, rtol=2e-2, atol=2e-2)
     w.check_status()
 
 
