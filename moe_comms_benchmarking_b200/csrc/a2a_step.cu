@@ -19,8 +19,9 @@
 //     and no barrier.  Every rank receives a one-packet header per token (routed to you or not), so a
 //     destination knows which rows to wait for; the destination's warp for that token unpacks the row
 //     into the ordinary receive buffers and sends the expert output straight back as packets, and the
-//     source sums them as they arrive.  All traffic of a token runs between the same block index on
-//     the ranks involved, and staging areas (two parities) are recycled on per-source credit words.
+//     source sums them as they arrive.  A token is served by a whole block (one 8-byte word per thread), all
+//     traffic of a token runs between the same block index on the ranks involved, and the staging areas
+//     (two parities) are recycled on per-source credit words.
 // Every wait is bounded and reports through the status words.
 #include <cuda_runtime.h>
 
@@ -84,35 +85,39 @@ __device__ __forceinline__ void ll_send_x(const McbCtx& c, const McbA2AStepArgs&
   }
 }
 
-// Source side of a layer: header to every rank, row / scales / metadata to the routed destinations.  One warp.
+// In packet mode a token is served by a whole BLOCK (steps are small, so blocks are plentiful, and a layer's
+// latency is a chain of dependent loads: with one 8-byte word per thread the chain is one load deep).
+
+// Source side of a layer: header to every rank, row / scales / metadata to the routed destinations.
 __device__ __forceinline__ void ll_dispatch_token(const McbCtx& c, const McbA2AStepArgs& a, const LLShape& s, int t,
-                                                  int epr, uint32_t par, uint32_t flag, int lane) {
+                                                  int epr, uint32_t par, uint32_t flag) {
+  const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31;
   const DestMask m = dest_mask(c, a, t, epr, lane);
-  for (int p = lane; p < c.world; p += 32) {
+  for (int p = tid; p < c.world; p += nthreads) {
     const uint32_t routed = (m.w[p >> 5] >> (p & 31)) & 1u;
     st_v4(c.heap_peer[p] + ll_x_slot(a, s, c.world, par, c.rank, t, 0), ll_pack(make_uint2(routed, (uint32_t)t), flag));
   }
   const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.x) + (uint64_t)t * a.hidden * 2;
   if (!a.fp8) {
-    for (int j = lane; j < s.xdata; j += 32) ll_send_x(c, a, s, m, par, t, 1 + j, ld_v2(xrow + (uint64_t)j * 8), flag);
+    for (int j = tid; j < s.xdata; j += nthreads) ll_send_x(c, a, s, m, par, t, 1 + j, ld_v2(xrow + (uint64_t)j * 8), flag);
   } else {
-    const int row_packs = a.hidden / 8;
-    for (int p0 = 0; p0 < row_packs; p0 += 32) {      // row_packs is a multiple of 32 (hidden % 256 == 0)
-      const int p = p0 + lane;
+    const int row_packs = a.hidden / 8;               // a multiple of 32 (hidden % 256 == 0): warps are all in or all out
+    for (int p = tid; p < row_packs; p += nthreads) {
       const uint4 v = ld_v4(xrow + (uint64_t)p * 16);
       float amax = pack_absmax(v);                     // 16 lanes hold one 128-value block
 #pragma unroll
       for (int sh = 8; sh >= 1; sh >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sh));
       const float scale = e4m3_scale(amax);
       ll_send_x(c, a, s, m, par, t, 1 + p, quant_pack_e4m3(v, scale), flag);
-      // lanes 0-15 hold block p0 / 16, lanes 16-31 the next one: one word carries both scales
+      // lanes 0-15 hold one block, lanes 16-31 the next one: one word carries both scales
       const float other = __shfl_sync(0xffffffffu, scale, 16);
       if (lane == 0)
-        ll_send_x(c, a, s, m, par, t, 1 + s.xdata + (p0 >> 5), make_uint2(__float_as_uint(scale), __float_as_uint(other)), flag);
+        ll_send_x(c, a, s, m, par, t, 1 + s.xdata + (p >> 5), make_uint2(__float_as_uint(scale), __float_as_uint(other)), flag);
     }
   }
-  // metadata row: chunk 0 = {stamp, token, id 0, weight 0}, chunk j = {id 2j-1, weight 2j-1, id 2j, weight 2j}
-  for (int j = lane; j < s.meta / 2; j += 32) {
+  // metadata row: chunk 0 = {stamp, token, id 0, weight 0}, chunk j = {id 2j-1, weight 2j-1, id 2j, weight 2j};
+  // taken from the top of the block so that it does not queue behind the row words of the low threads
+  for (int j = nthreads - 1 - tid; j < s.meta / 2; j += nthreads) {
     const int k0 = j == 0 ? 0 : 2 * j - 1, k1 = 2 * j;
     const long long tb = (long long)t * a.topk;
     const uint32_t id0 = k0 < a.topk ? (uint32_t)a.topk_idx[tb + k0] : 0xffffffffu;
@@ -134,9 +139,10 @@ __device__ __forceinline__ void ll_dispatch_token(const McbCtx& c, const McbA2AS
 
 // Destination side: wait for the header of (source, token); if the token is routed here, unpack its row
 // into the ordinary receive buffers and send the expert output (the row itself for the identity expert
-// in bf16, the y buffer otherwise) back to the source.  One warp.
+// in bf16, the y buffer otherwise) back to the source.
 __device__ __forceinline__ void ll_serve_token(const McbCtx& c, const McbA2AStepArgs& a, const LLShape& s, int src, int t,
-                                               uint32_t par, uint32_t flag, int lane) {
+                                               uint32_t par, uint32_t flag) {
+  const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31;
   uint32_t routed = 0;
   if (lane == 0) routed = ll_wait(c, c.heap_local + ll_x_slot(a, s, c.world, par, src, t, 0), flag, MCB_SITE_A2A_STEP).x;
   routed = __shfl_sync(0xffffffffu, routed, 0);
@@ -149,75 +155,64 @@ __device__ __forceinline__ void ll_serve_token(const McbCtx& c, const McbA2AStep
   const uint8_t* yrow = c.heap_local + a.y_off + (uint64_t)par * a.y_par_stride + row * (uint64_t)a.hidden * 2;
   const int body = s.xdata + s.scales + s.meta;
   const bool echo = !a.fp8 && a.y_off == a.recv_x_off;     // identity expert on bf16 rows: the row is its own output
-  // poll 4 packets per lane at a time, wait only for those not there yet
-  for (int j0 = lane; j0 < body; j0 += 128) {
-    uint4 v[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = j0 + u * 32;
-      if (j < body) v[u] = ld_v4_volatile(c.heap_local + ll_x_slot(a, s, c.world, par, src, t, 1 + j));
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = j0 + u * 32;
-      if (j >= body) continue;
-      uint2 d = make_uint2(v[u].x, v[u].z);
-      if (v[u].y != flag || v[u].w != flag)
-        d = ll_wait(c, c.heap_local + ll_x_slot(a, s, c.world, par, src, t, 1 + j), flag, MCB_SITE_A2A_STEP);
-      if (j < s.xdata) {
-        st_v2(rx + (uint64_t)j * 8, d);
-        if (echo) st_v4(c.heap_peer[src] + ll_y_slot(a, s, c.world, par, c.rank, t, j), ll_pack(d, flag));
-      } else if (j < s.xdata + s.scales) {
-        st_v2(rs + (uint64_t)(j - s.xdata) * 8, d);
-      } else {
-        st_v2(rm + (uint64_t)(j - s.xdata - s.scales) * 8, d);
-      }
+  if (!echo)     // the expert output is a bf16 row of its own: it can leave before the row has arrived
+    for (int j = tid; j < s.yw; j += nthreads)
+      st_v4(c.heap_peer[src] + ll_y_slot(a, s, c.world, par, c.rank, t, j), ll_pack(ld_v2(yrow + (uint64_t)j * 8), flag));
+  for (int j = tid; j < body; j += nthreads) {
+    const uint2 d = ll_wait(c, c.heap_local + ll_x_slot(a, s, c.world, par, src, t, 1 + j), flag, MCB_SITE_A2A_STEP);
+    if (j < s.xdata) {
+      if (echo) st_v4(c.heap_peer[src] + ll_y_slot(a, s, c.world, par, c.rank, t, j), ll_pack(d, flag));
+      st_v2(rx + (uint64_t)j * 8, d);
+    } else if (j < s.xdata + s.scales) {
+      st_v2(rs + (uint64_t)(j - s.xdata) * 8, d);
+    } else {
+      st_v2(rm + (uint64_t)(j - s.xdata - s.scales) * 8, d);
     }
   }
-  if (!echo)     // the expert output is a bf16 row of its own
-    for (int j = lane; j < s.yw; j += 32)
-      st_v4(c.heap_peer[src] + ll_y_slot(a, s, c.world, par, c.rank, t, j), ll_pack(ld_v2(yrow + (uint64_t)j * 8), flag));
 }
 
-// Source side again: sum the expert outputs of every destination as their packets arrive.  One warp.
+__device__ __forceinline__ int pop_dest(DestMask& m) {
+#pragma unroll
+  for (int wi = 0; wi < 3; ++wi)
+    if (m.w[wi]) {
+      const int b = __ffs(m.w[wi]) - 1;
+      m.w[wi] &= m.w[wi] - 1;
+      return wi * 32 + b;
+    }
+  return -1;
+}
+
+// Source side again: sum the expert outputs of every destination as their packets arrive (four
+// destinations' packets in flight per thread).
 __device__ __forceinline__ void ll_combine_token(const McbCtx& c, const McbA2AStepArgs& a, const LLShape& s, int t,
-                                                 int epr, uint32_t par, uint32_t flag, int lane) {
+                                                 int epr, uint32_t par, uint32_t flag) {
+  const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31;
   const DestMask m = dest_mask(c, a, t, epr, lane);
   uint8_t* orow = reinterpret_cast<uint8_t*>(a.out) + (uint64_t)t * a.hidden * 2;
-  for (int j0 = lane; j0 < s.yw; j0 += 128) {
-    float acc[4][4];
+  for (int j = tid; j < s.yw; j += nthreads) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    DestMask rest = m;
+    for (;;) {
+      int d[4];
+      d[0] = pop_dest(rest);
+      if (d[0] < 0) break;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
-#pragma unroll 1
-    for (int wi = 0; wi < 3; ++wi) {
-      uint32_t bits = m.w[wi];
-      while (bits) {
-        const int d = wi * 32 + __ffs(bits) - 1;
-        bits &= bits - 1;
-        uint4 v[4];
+      for (int u = 1; u < 4; ++u) d[u] = pop_dest(rest);
+      uint4 v[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int j = j0 + u * 32;
-          if (j < s.yw) v[u] = ld_v4_volatile(c.heap_local + ll_y_slot(a, s, c.world, par, d, t, j));
-        }
+      for (int u = 0; u < 4; ++u)
+        if (d[u] >= 0) v[u] = ld_v4_volatile(c.heap_local + ll_y_slot(a, s, c.world, par, d[u], t, j));
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int j = j0 + u * 32;
-          if (j >= s.yw) continue;
-          uint2 w = make_uint2(v[u].x, v[u].z);
-          if (v[u].y != flag || v[u].w != flag)
-            w = ll_wait(c, c.heap_local + ll_y_slot(a, s, c.world, par, d, t, j), flag, MCB_SITE_A2A_STEP);
-          acc[u][0] += bf16_lo(w.x); acc[u][1] += bf16_hi(w.x);
-          acc[u][2] += bf16_lo(w.y); acc[u][3] += bf16_hi(w.y);
-        }
+      for (int u = 0; u < 4; ++u) {
+        if (d[u] < 0) continue;
+        uint2 w = make_uint2(v[u].x, v[u].z);
+        if (v[u].y != flag || v[u].w != flag)
+          w = ll_wait(c, c.heap_local + ll_y_slot(a, s, c.world, par, d[u], t, j), flag, MCB_SITE_A2A_STEP);
+        acc[0] += bf16_lo(w.x); acc[1] += bf16_hi(w.x);
+        acc[2] += bf16_lo(w.y); acc[3] += bf16_hi(w.y);
       }
     }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int j = j0 + u * 32;
-      if (j < s.yw)
-        st_v2(orow + (uint64_t)j * 8, make_uint2(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3])));
-    }
+    st_v2(orow + (uint64_t)j * 8, make_uint2(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3])));
   }
 }
 
@@ -258,28 +253,25 @@ __global__ void __launch_bounds__(512) a2a_step_kernel(const __grid_constant__ M
   const bool ll = W > 1 && a.ll_rows > 0 && valid > 0 && valid <= a.ll_rows && (!a.fp8 || a.hidden % 256 == 0);
   if (bid == 0 && tid == 0) a.step_meta[6] = ll ? 1 : 0;
   if (ll) {
-    // ---- packet mode: global token g belongs to warp slot g % (blocks * warps) on every rank ----
-    int nb = (valid + nwarps - 1) / nwarps;
-    nb = nb > (int)gridDim.x ? (int)gridDim.x : nb;
+    // ---- packet mode: global token g belongs to block g % blocks on every rank ----
+    const int nb = valid < (int)gridDim.x ? valid : (int)gridDim.x;
     if (bid < nb) {
-      const int slots = nb * nwarps, slot = bid * nwarps + warp;
       const int epr_ll = a.num_experts / W;
       const int offset = s_prefix[c.rank];
       const uint32_t cb = *epoch_ptr(c, MCB_SITE_A2A_STEP_CREDIT, bid);
+      const int t0 = ((bid - offset) % nb + nb) % nb;      // first own token with (offset + t) % nb == bid
       for (int l = 0; l < L; ++l) {
         const uint32_t par = (layer_base + (uint32_t)l) & 1u;
         const uint32_t flag = layer_base + (uint32_t)l + 1u;
         // the staging areas of this parity were read last in layer l - 2
         if (l >= 2) credit_wait(c, a.credit_off, cb + (uint32_t)l - 1u, MCB_SITE_A2A_STEP_CREDIT);
-        // first own token with (offset + t) % slots == slot
-        const int t0 = ((slot - offset) % slots + slots) % slots;
-        for (int t = t0; t < n; t += slots) ll_dispatch_token(c, a, shp, t, epr_ll, par, flag, lane);
-        for (int g = slot; g < valid; g += slots) {
+        for (int t = t0; t < n; t += nb) ll_dispatch_token(c, a, shp, t, epr_ll, par, flag);
+        for (int g = bid; g < valid; g += nb) {
           int src = 0;
           while (src + 1 < W && s_prefix[src + 1] <= g) ++src;
-          ll_serve_token(c, a, shp, src, g - s_prefix[src], par, flag, lane);
+          ll_serve_token(c, a, shp, src, g - s_prefix[src], par, flag);
         }
-        for (int t = t0; t < n; t += slots) ll_combine_token(c, a, shp, t, epr_ll, par, flag, lane);
+        for (int t = t0; t < n; t += nb) ll_combine_token(c, a, shp, t, epr_ll, par, flag);
         __syncthreads();
         credit_publish(c, a.credit_off, cb + (uint32_t)l + 1u);
       }

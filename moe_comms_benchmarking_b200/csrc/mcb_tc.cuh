@@ -49,11 +49,14 @@ __device__ __forceinline__ uint64_t now_ns() {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const Abort& ab, uint32_t where) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = now_ns();
-  for (;;) {
+  for (uint32_t round = 0;; ++round) {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*ab.flag) return false;
+    // The checks below read global memory and the global timer (about a microsecond during which this
+    // thread does not see the barrier flip): one round in 32 is enough for a bound counted in seconds.
+    if ((round & 31u) != 31u) continue;
     // Once any kernel on this rank has recorded an error, later waits give up at once, so the rest
     // of a captured multi-layer step drains quickly instead of timing out launch by launch.
     if (ab.status && *reinterpret_cast<volatile uint32_t*>(ab.status) != 0u) {

