@@ -216,68 +216,41 @@ __device__ __forceinline__ void ll_combine_token(const McbCtx& c, const McbA2ASt
   }
 }
 
-template <bool EMU>
-__global__ void __launch_bounds__(512) a2a_step_kernel(const __grid_constant__ McbCtx ctx_p,
-                                                       const __grid_constant__ McbA2AStepArgs args_p,
-                                                       const McbCtx* ectx, const McbA2AStepArgs* eargs) {
-  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
-  const McbA2AStepArgs& a = EMU ? eargs[blockIdx.y] : args_p;
-  __shared__ int s_prefix[MCB_MAX_RANKS + 1];
-  __shared__ int s_cnt[MCB_MAX_RANKS];
-  __shared__ int s_max;
+// Packet-mode layers of a step: global token g belongs to block g % blocks on every rank.  Kept out of line
+// so that the two modes do not share one register allocation.
+__device__ __noinline__ void packet_layers(const McbCtx& c, const McbA2AStepArgs& a, const LLShape& shp, const int* s_prefix,
+                                           int n, int valid, uint32_t layer_base) {
+  const int tid = threadIdx.x, bid = blockIdx.x;
+  const int W = c.world, L = a.num_layers;
+  const int nb = valid < (int)gridDim.x ? valid : (int)gridDim.x;
+  if (bid >= nb) return;
+  const int epr_ll = a.num_experts / W;
+  const int offset = s_prefix[c.rank];
+  const uint32_t cb = *epoch_ptr(c, MCB_SITE_A2A_STEP_CREDIT, bid);
+  const int t0 = ((bid - offset) % nb + nb) % nb;      // first own token with (offset + t) % nb == bid
+  for (int l = 0; l < L; ++l) {
+    const uint32_t par = (layer_base + (uint32_t)l) & 1u;
+    const uint32_t flag = layer_base + (uint32_t)l + 1u;
+    // the staging areas of this parity were read last in layer l - 2
+    if (l >= 2) credit_wait(c, a.credit_off, cb + (uint32_t)l - 1u, MCB_SITE_A2A_STEP_CREDIT);
+    for (int t = t0; t < n; t += nb) ll_dispatch_token(c, a, shp, t, epr_ll, par, flag);
+    for (int g = bid; g < valid; g += nb) {
+      int src = 0;
+      while (src + 1 < W && s_prefix[src + 1] <= g) ++src;
+      ll_serve_token(c, a, shp, src, g - s_prefix[src], par, flag);
+    }
+    for (int t = t0; t < n; t += nb) ll_combine_token(c, a, shp, t, epr_ll, par, flag);
+    __syncthreads();
+    credit_publish(c, a.credit_off, cb + (uint32_t)l + 1u);
+  }
+  if (tid == 0) *epoch_ptr(c, MCB_SITE_A2A_STEP_CREDIT, bid) = cb + (uint32_t)L;
+}
+
+// Barrier-mode layers of a step: push -> one block-matched barrier -> pull + fp32 sum.  Out of line, as above.
+__device__ __noinline__ void barrier_layers(const McbCtx& c, const McbA2AStepArgs& a, int n, int ep_max, uint32_t layer_base) {
   const int tid = threadIdx.x, bid = blockIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nwarps = blockDim.x >> 5;
   const int W = c.world, L = a.num_layers;
-  pdl_wait();
-  pdl_launch_dependents();
-  volatile uint32_t* state = a.state;
-  const uint32_t step_seq = state[MCB_STATE_STEP_SEQ], layer_base = state[MCB_STATE_LAYER_BASE];
-  const int n = step_count_exchange(c, MCB_SITE_A2A_STEP_META, a.counts_off, step_seq, *a.n_local, a.cap, s_cnt,
-                                    s_prefix, &s_max);
-  const int ep_max = s_max;
-  if (bid == 0 && tid == 0) {
-    a.step_meta[0] = s_prefix[W];
-    a.step_meta[1] = s_prefix[c.rank];
-    a.step_meta[2] = ep_max;
-    a.step_meta[4] = (int)(step_seq + 1u);
-    a.step_meta[5] = L > 0 ? (int)((layer_base + (uint32_t)L - 1u) & 1u) : 0;
-    a.step_meta[7] = (int)(layer_base + (uint32_t)L);     // stamp of the last layer's rows
-  }
-  const int valid = s_prefix[W];
-  LLShape shp;
-  shp.xdata = a.fp8 ? a.hidden / 8 : a.hidden / 4;
-  shp.scales = a.fp8 ? a.hidden / 256 : 0;
-  shp.meta = (int)(a.meta_row_bytes >> 3);
-  shp.xw = 1 + shp.xdata + shp.scales + shp.meta;
-  shp.yw = a.hidden / 4;
-  const bool ll = W > 1 && a.ll_rows > 0 && valid > 0 && valid <= a.ll_rows && (!a.fp8 || a.hidden % 256 == 0);
-  if (bid == 0 && tid == 0) a.step_meta[6] = ll ? 1 : 0;
-  if (ll) {
-    // ---- packet mode: global token g belongs to block g % blocks on every rank ----
-    const int nb = valid < (int)gridDim.x ? valid : (int)gridDim.x;
-    if (bid < nb) {
-      const int epr_ll = a.num_experts / W;
-      const int offset = s_prefix[c.rank];
-      const uint32_t cb = *epoch_ptr(c, MCB_SITE_A2A_STEP_CREDIT, bid);
-      const int t0 = ((bid - offset) % nb + nb) % nb;      // first own token with (offset + t) % nb == bid
-      for (int l = 0; l < L; ++l) {
-        const uint32_t par = (layer_base + (uint32_t)l) & 1u;
-        const uint32_t flag = layer_base + (uint32_t)l + 1u;
-        // the staging areas of this parity were read last in layer l - 2
-        if (l >= 2) credit_wait(c, a.credit_off, cb + (uint32_t)l - 1u, MCB_SITE_A2A_STEP_CREDIT);
-        for (int t = t0; t < n; t += nb) ll_dispatch_token(c, a, shp, t, epr_ll, par, flag);
-        for (int g = bid; g < valid; g += nb) {
-          int src = 0;
-          while (src + 1 < W && s_prefix[src + 1] <= g) ++src;
-          ll_serve_token(c, a, shp, src, g - s_prefix[src], par, flag);
-        }
-        for (int t = t0; t < n; t += nb) ll_combine_token(c, a, shp, t, epr_ll, par, flag);
-        __syncthreads();
-        credit_publish(c, a.credit_off, cb + (uint32_t)l + 1u);
-      }
-      if (tid == 0) *epoch_ptr(c, MCB_SITE_A2A_STEP_CREDIT, bid) = cb + (uint32_t)L;
-    }
-  }
   // One warp per token; as many blocks as the largest rank needs, the same on every rank.
   int nact = (ep_max + nwarps - 1) / nwarps;
   nact = nact > (int)gridDim.x ? (int)gridDim.x : nact;
@@ -290,7 +263,7 @@ __global__ void __launch_bounds__(512) a2a_step_kernel(const __grid_constant__ M
   const uint8_t* x = reinterpret_cast<const uint8_t*>(a.x);
   uint8_t* out = reinterpret_cast<uint8_t*>(a.out);
 
-  if (!ll && bid < nact) {
+  if (bid < nact) {
     uint32_t ep = *epoch_ptr(c, MCB_SITE_A2A_STEP, bid);
     for (int l = 0; l < L; ++l) {
       const uint32_t par = (layer_base + (uint32_t)l) & 1u;
@@ -428,6 +401,49 @@ __global__ void __launch_bounds__(512) a2a_step_kernel(const __grid_constant__ M
     if (tid == 0) *epoch_ptr(c, MCB_SITE_A2A_STEP, bid) = ep;
   }
 
+}
+
+template <bool EMU>
+__global__ void __launch_bounds__(512) a2a_step_kernel(const __grid_constant__ McbCtx ctx_p,
+                                                       const __grid_constant__ McbA2AStepArgs args_p,
+                                                       const McbCtx* ectx, const McbA2AStepArgs* eargs) {
+  const McbCtx& c = EMU ? ectx[blockIdx.y] : ctx_p;
+  const McbA2AStepArgs& a = EMU ? eargs[blockIdx.y] : args_p;
+  __shared__ int s_prefix[MCB_MAX_RANKS + 1];
+  __shared__ int s_cnt[MCB_MAX_RANKS];
+  __shared__ int s_max;
+  const int tid = threadIdx.x, bid = blockIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int W = c.world, L = a.num_layers;
+  pdl_wait();
+  pdl_launch_dependents();
+  volatile uint32_t* state = a.state;
+  const uint32_t step_seq = state[MCB_STATE_STEP_SEQ], layer_base = state[MCB_STATE_LAYER_BASE];
+  const int n = step_count_exchange(c, MCB_SITE_A2A_STEP_META, a.counts_off, step_seq, *a.n_local, a.cap, s_cnt,
+                                    s_prefix, &s_max);
+  const int ep_max = s_max;
+  if (bid == 0 && tid == 0) {
+    a.step_meta[0] = s_prefix[W];
+    a.step_meta[1] = s_prefix[c.rank];
+    a.step_meta[2] = ep_max;
+    a.step_meta[4] = (int)(step_seq + 1u);
+    a.step_meta[5] = L > 0 ? (int)((layer_base + (uint32_t)L - 1u) & 1u) : 0;
+    a.step_meta[7] = (int)(layer_base + (uint32_t)L);     // stamp of the last layer's rows
+  }
+  const int valid = s_prefix[W];
+  LLShape shp;
+  shp.xdata = a.fp8 ? a.hidden / 8 : a.hidden / 4;
+  shp.scales = a.fp8 ? a.hidden / 256 : 0;
+  shp.meta = (int)(a.meta_row_bytes >> 3);
+  shp.xw = 1 + shp.xdata + shp.scales + shp.meta;
+  shp.yw = a.hidden / 4;
+  const bool ll = W > 1 && a.ll_rows > 0 && valid > 0 && valid <= a.ll_rows && (!a.fp8 || a.hidden % 256 == 0);
+  if (bid == 0 && tid == 0) a.step_meta[6] = ll ? 1 : 0;
+  if (ll) {
+    packet_layers(c, a, shp, s_prefix, n, valid, layer_base);
+  } else {
+    barrier_layers(c, a, n, ep_max, layer_base);
+  }
   // ---- the last block out advances the sequence words ----
   __syncthreads();
   if (tid == 0) {
