@@ -53,6 +53,9 @@ def parse_args(argv=None):
     p.add_argument("--fused-sweep", default="64,512,4096",
                    help="global batches of the real-expert (fused SwiGLU) path reported under 'fused_ms_by_global_batch' "
                         "(empty = skip)")
+    p.add_argument("--a2a-sweep", default="1,64,512,8192",
+                   help="global batches at which the all-to-all dispatcher is timed too (run.py --impl a2a in a child "
+                        "job: graph replays back to back); empty = skip")
     p.add_argument("--fused-weight-gb", type=float, default=40.0, help="GPU memory for the expert weights of that path")
     return p.parse_args(argv)
 
@@ -85,10 +88,9 @@ def pinned_inputs(hidden, idx, w):
     return hidden.cpu().pin_memory(), idx.cpu().pin_memory(), w.cpu().pin_memory()
 
 
-def run_fused_child(world, batches, args):
-    """Times the real-expert path (config: 512 experts, SwiGLU FFN 1024 -> 1024 -> 1024 per expert, bf16 weights
-    N(0, 0.02^2), 88 layers) with ``run.py --impl fused`` in a child job on the same GPUs; returns
-    ({global batch: ms per step}, details)."""
+def run_child(world, impl, batches, extra):
+    """Runs ``run.py --impl <impl>`` as a child job on the same GPUs (this job's ranks wait on the host
+    meanwhile) and returns {global batch: ms per 88-layer step} from its CSV."""
     import csv
     import socket
     import subprocess
@@ -96,21 +98,27 @@ def run_fused_child(world, batches, args):
     with socket.socket() as sk:
         sk.bind(("127.0.0.1", 0))
         port = sk.getsockname()[1]
-    out = os.path.join(tempfile.mkdtemp(prefix="mcb_fused_"), "fused.csv")
+    out = os.path.join(tempfile.mkdtemp(prefix=f"mcb_{impl}_"), "child.csv")
     env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE",
                                                            "GROUP_RANK", "ROLE_RANK", "MASTER_PORT", "TORCHELASTIC_RUN_ID")}
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
-           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "run.py"), "--impl", "fused", "--batch-sizes",
-           ",".join(str(b) for b in batches), "--num-layers", str(NUM_LAYERS), "--reps", "5", "--warmup", "3",
-           "--weight-budget-gb", str(args.fused_weight_gb), "--out", out]
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "run.py"), "--impl", impl, "--batch-sizes",
+           ",".join(str(b) for b in batches), "--num-layers", str(NUM_LAYERS), "--out", out] + extra
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
     if res.returncode != 0 or not os.path.exists(out):
         raise RuntimeError(f"child job failed (rc {res.returncode}): {(res.stdout + res.stderr)[-300:]}")
     ms = {}
     with open(out) as f:
         for row in csv.DictReader(f):
-            if row["impl"] == "fused" and row["phase"] == "decode_step":
+            if row["impl"] == impl and row["phase"] == "decode_step":
                 ms[row["global_B"]] = round(float(row["latency_us"]) / 1e3, 4)
+    return ms
+
+
+def run_fused_child(world, batches, args):
+    """Times the real-expert path (config: 512 experts, SwiGLU FFN 1024 -> 1024 -> 1024 per expert, bf16 weights
+    N(0, 0.02^2), 88 layers) with ``run.py --impl fused``; returns ({global batch: ms per step}, details)."""
+    ms = run_child(world, "fused", batches, ["--reps", "5", "--warmup", "3", "--weight-budget-gb", str(args.fused_weight_gb)])
     experts_per_rank = 512 // world
     detail = {"kernels_per_step": 1 + NUM_LAYERS, "protocol": "run.py --impl fused: graph replays back to back, max over ranks",
               "weights_mb_per_layer_and_rank": round(experts_per_rank * 3 * 1024 * 1024 * 2 / 1e6, 1),
@@ -165,16 +173,23 @@ def run_native(args):
     # the headline, never part of it.  It runs as a CHILD job through the repository's own driver
     # (run.py --impl fused) while this job's ranks wait on the host, so that nothing that happens there
     # can cost the headline line.
-    fused_ms, fused_detail = {}, {}
+    fused_ms, fused_detail, a2a_ms = {}, {}, {}
     fused_sweep = [int(b) for b in args.fused_sweep.split(",") if b.strip()]
-    if fused_sweep:
+    a2a_sweep = [int(b) for b in args.a2a_sweep.split(",") if b.strip()]
+    if fused_sweep or a2a_sweep:
         import datetime
         store = dist.distributed_c10d._get_default_store()
         if rank == 0:
-            try:
-                fused_ms, fused_detail = run_fused_child(world, fused_sweep, args)
-            except Exception as e:
-                fused_detail = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+            if fused_sweep:
+                try:
+                    fused_ms, fused_detail = run_fused_child(world, fused_sweep, args)
+                except Exception as e:
+                    fused_detail = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+            if a2a_sweep:       # the all-to-all dispatcher (the role DeepEP has in the reference), identity expert
+                try:
+                    a2a_ms = run_child(world, "a2a", a2a_sweep, ["--reps", "10", "--warmup", "3"])
+                except Exception as e:
+                    a2a_ms = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
             store.set("bench/fused_done", "1")
         else:
             store.wait(["bench/fused_done"], datetime.timedelta(seconds=900))    # host-side: the GPUs stay free
@@ -205,6 +220,7 @@ def run_native(args):
             "gpu_launches": launches,
             "sweep_ms_by_global_batch": {k: round(v, 4) for k, v in sweep_ms.items()},
             "fused_ms_by_global_batch": fused_ms, "fused_detail": fused_detail,
+            "a2a_ms_by_global_batch": a2a_ms,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -170,3 +170,6 @@ def test_bench_contract_one_gpu():
     assert line["n_gpus"] == 1 and line["steps"] == 3 and line["gpu_launches"] == 3 * 1      # one persistent kernel per step
     assert line["value"] > 0 and line["e2e"]["value"] >= line["value"] * 0.5
     assert line["e2e"]["h2d_bytes_per_step"] == 8192 * 2312 + 4
+    # the real-expert path and the all-to-all dispatcher are timed by child jobs and reported beside the headline
+    assert set(line["fused_ms_by_global_batch"]) == {"64", "512", "4096"}, line.get("fused_detail")
+    assert set(line["a2a_ms_by_global_batch"]) == {"1", "64", "512", "8192"}, line["a2a_ms_by_global_batch"]
