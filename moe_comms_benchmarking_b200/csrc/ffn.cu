@@ -38,15 +38,24 @@ moe_layer_kernel(const __grid_constant__ McbLayerArgs p_, const McbLayerArgs* ea
   const McbLayerArgs& p = EMU ? eargs[blockIdx.y] : p_;
   const McbCtx& c = p.ctx;
   uint32_t ll_launch = 0;
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+  if (tracing) p.trace[0] = globaltimer_ns();
   agv_device<MCB_SITE_FC1_FUSED>(c, p.agv, ll_launch);      // waits for the previous kernel first
+  if (tracing) p.trace[1] = globaltimer_ns();
   // The arrival counter is back at zero whenever a launch has ended (its last block resets it).
   uint32_t* arrivals = epoch_ptr(c, MCB_SITE_LAYER, 1);
   grid_sync(c, arrivals, gridDim.x);
+  if (tracing) p.trace[2] = globaltimer_ns();
   route_device(p.route);
+  if (tracing) p.trace[3] = globaltimer_ns();
   grid_sync(c, arrivals, 2u * gridDim.x);
+  if (tracing) p.trace[4] = globaltimer_ns();
   ffn_device(p.ffn);
+  if (tracing) p.trace[5] = globaltimer_ns();
   grid_sync(c, arrivals, 3u * gridDim.x);                   // every y row is written before any is summed
+  if (tracing) p.trace[6] = globaltimer_ns();
   combine_body(c, p.cmb, ll_launch);      // partial sums alternate between two buffers, layer by layer
+  if (tracing) p.trace[7] = globaltimer_ns();
   launch_end(c, MCB_SITE_FC1_FUSED, ll_launch, arrivals);
 }
 

@@ -113,5 +113,9 @@ typedef struct alignas(64) {
   McbRouteArgs route;
   McbFfnArgs ffn;
   McbCombineArgs cmb;
+  // Optional phase trace (null = off): block 0 stores the global timer (ns) at kernel entry and after
+  // dispatch, grid barrier, routing, grid barrier, experts, grid barrier, combine (8 words).
+  unsigned long long* trace;
+  unsigned long long reserved0;
 } McbLayerArgs;
 #endif

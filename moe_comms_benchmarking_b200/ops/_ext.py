@@ -159,6 +159,7 @@ class McbLayerArgs(C.Structure):
     phases (64-byte aligned as a whole)."""
     _fields_ = [
         ("ctx", McbCtx), ("agv", McbAgvArgs), ("route", McbRouteArgs), ("ffn", McbFfnArgs), ("cmb", McbCombineArgs),
+        ("trace", _vp), ("reserved0", _u64),
     ]
 
 

@@ -323,10 +323,12 @@ class MoeLayerPlan:
     count exchange and ``n`` layers natively (layer l uses set l % sets)."""
 
     def __init__(self, heap: SymmetricHeap, agv, route: RoutePlan, ffns: list[ExpertFfnPlan], combine: ExpertCombinePlan,
-                 meta, grid: int = NUM_SMS):
+                 meta, grid: int = NUM_SMS, trace: bool = False):
         if not (1 <= grid <= NUM_SMS):
             raise ValueError("the layer kernel needs all its blocks resident at once: grid <= number of SMs")
         self.heap, self.agv, self.route, self.ffns, self.combine, self.meta, self.grid = heap, agv, route, ffns, combine, meta, grid
+        # phase trace: 8 global-timer stamps of block 0 of the LAST layer launched (see phase_times)
+        self.trace = torch.zeros(8, dtype=torch.int64, device=heap.device) if trace else None
         self._raw, self._addr, self._stride = _aligned_layer_args(len(ffns))
         self._ctx_version = None
         self._fill()
@@ -340,11 +342,22 @@ class MoeLayerPlan:
             C.memmove(C.addressof(p.route), C.addressof(self.route.args), C.sizeof(_ext.McbRouteArgs))
             C.memmove(C.addressof(p.ffn), C.addressof(f.args), C.sizeof(_ext.McbFfnArgs))
             C.memmove(C.addressof(p.cmb), C.addressof(self.combine.args), C.sizeof(_ext.McbCombineArgs))
+            p.trace = self.trace.data_ptr() if self.trace is not None else None
         self._ctx_version = id(ctx)
 
     def _sync_ctx(self):
         if self._ctx_version != id(self.heap.ctx()):      # the heap's context was rebuilt (e.g. a new timeout)
             self._fill()
+
+    PHASES = ("dispatch", "grid barrier", "routing", "grid barrier", "experts", "grid barrier", "combine")
+
+    def phase_times(self):
+        """[(phase, microseconds)] of the last layer launched, as block 0 saw it (needs ``trace=True``; read after
+        a synchronize)."""
+        if self.trace is None:
+            raise RuntimeError("built without trace=True")
+        t = self.trace.cpu().tolist()
+        return [(name, (t[i + 1] - t[i]) / 1e3) for i, name in enumerate(self.PHASES)]
 
     def args(self, s: int = 0) -> "_ext.McbLayerArgs":
         return _ext.McbLayerArgs.from_address(self._addr + s * self._stride)

@@ -44,7 +44,7 @@ class FusedExpertDispatcher(Dispatcher):
                  threads: int = DEFAULT_THREADS, pdl: bool = True, transport: str = "auto", ll_rows: int = -1,
                  num_layers: int = 88, weight_budget_gb: float = 64.0, weight_seed: int = 7,
                  fuse_combine: bool = True, fuse_dispatch: bool = True, coop_pdl: bool = False,
-                 layer_kernel: bool = True, device=None):
+                 layer_kernel: bool = True, phase_trace: bool = False, device=None):
         super().__init__(cfg, group, device)
         self.heap, self._own_heap = heap, heap is None
         self.num_sms, self.threads, self.pdl, self.transport = int(num_sms), int(threads), bool(pdl), transport
@@ -54,6 +54,7 @@ class FusedExpertDispatcher(Dispatcher):
         self.coop_pdl = bool(coop_pdl)   # cooperative + programmatic dependent launch on the fused kernel
         self.fuse_dispatch = bool(fuse_dispatch)
         self.layer_kernel = bool(layer_kernel)
+        self.phase_trace = bool(phase_trace) and self.layer_kernel
         self.kernel_launches_per_step = lambda nl: 1 + (
             1 if self.layer_kernel else 5 - int(self.fuse_combine) - 2 * int(self.fuse_dispatch)) * nl
 
@@ -106,7 +107,8 @@ class FusedExpertDispatcher(Dispatcher):
                                               self.step_metadata, cap, grid=NUM_SMS)
         if self.layer_kernel:
             self.ffn = [ExpertFfnPlan(w, self.route, self.agv_h.tensor, self.act, self.y, st) for w in self.weights]
-            self.layer_plan = MoeLayerPlan(h, self.agv_plan, self.route_plan, self.ffn, self.combine_plan, self.meta_plan)
+            self.layer_plan = MoeLayerPlan(h, self.agv_plan, self.route_plan, self.ffn, self.combine_plan, self.meta_plan,
+                                           trace=self.phase_trace)
         else:
             self.fc1 = [GroupedGemmPlan(_ext.GEMM_FC1, w.map_gate_up, self.route, self.agv_h.tensor, self.act, 2 * I, H, st)
                         for w in self.weights]

@@ -76,6 +76,9 @@ def parse_args(argv=None):
                    help="dense / a2a: one kernel per operation (1 + 2 x layers / 2 x layers launches) instead of one per decode step")
     p.add_argument("--groups", type=int, default=1,
                    help="dense: pipeline groups of the persistent step kernel (1 = none)")
+    p.add_argument("--phase-times", action="store_true",
+                   help="fused: after each batch size print how long block 0 of rank 0 spent in each phase of the last "
+                        "layer (dispatch, routing, experts, combine and the grid barriers between them)")
     p.add_argument("--no-layer-kernel", action="store_true",
                    help="fused: the two-kernel form with tokens as the M operand instead of one kernel per layer")
     p.add_argument("--dense-num-sms", type=int, default=148, help="CTA cap of the dense kernels")
@@ -154,7 +157,7 @@ def build_dispatchers(names, cfg, group, args, device, sms_list):
                                              weight_budget_gb=args.weight_budget_gb,
                                              fuse_combine=not args.no_fuse_combine,
                                              fuse_dispatch=not args.no_fuse_dispatch, coop_pdl=args.coop_pdl,
-                                             layer_kernel=not args.no_layer_kernel))
+                                             layer_kernel=not args.no_layer_kernel, phase_trace=args.phase_times))
         elif n == "nccl":
             from moe_comms_benchmarking_b200.parallel.nccl import NCCLDispatcher
             out.append(NCCLDispatcher(cfg, group))
@@ -280,6 +283,10 @@ def main(argv=None) -> int:
                         (_, step_us), used_graph = timed_with_fallback(lambda: b.decode_step(nl), group, args.warmup,
                                                                        args.reps, args.timing, rank)
                     b.check_health()
+                    if args.phase_times and getattr(b, "phase_trace", False):
+                        torch.cuda.synchronize()
+                        say(f"    phases of the last layer (block 0, rank {rank}): "
+                            + ", ".join(f"{n} {us:.1f}us" for n, us in b.layer_plan.phase_times())) if rank == 0 else None
                 else:
                     import time
                     for _ in range(args.warmup):
