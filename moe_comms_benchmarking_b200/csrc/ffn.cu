@@ -84,7 +84,7 @@ static bool configure_ffn_kernels() {
 static int check_ffn_args(const McbFfnArgs* a) {
   if (!a || !a->x || !a->pair_token || !a->expert_offset || !a->max_rows || !a->act || !a->y || !a->ffn_done) return 1;
   if (!a->w1 || !a->w2 || (reinterpret_cast<uintptr_t>(a->w1) & 15) || (reinterpret_cast<uintptr_t>(a->w2) & 15)) return 1;
-  if (a->num_local_experts < 1 || a->hidden < 128 || a->hidden % 128 || a->intermediate < 128 || a->intermediate % 128) return 1;
+  if (a->num_local_experts < 1 || a->num_local_experts > kFfnMaxExperts || a->hidden < 128 || a->hidden % 128 || a->intermediate < 128 || a->intermediate % 128) return 1;
   if (a->x_row_bytes & 15) return 1;
   return 0;
 }

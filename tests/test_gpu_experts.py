@@ -83,11 +83,13 @@ def test_route_fc1_fc2_combine_against_oracle(world1, T, E, K, H, I):
 
 
 @pytest.mark.parametrize("T,E,K,H,I,grid", [(64, 16, 4, 256, 128, 148), (37, 4, 2, 1024, 1024, 24), (700, 2, 2, 512, 256, 5),
-                                            (3, 8, 2, 256, 128, 148), (4500, 8, 4, 256, 128, 148)])
+                                            (3, 8, 2, 256, 128, 148), (4500, 8, 4, 256, 128, 148),
+                                            (400, 8, 2, 256, 256, 3), (400, 8, 2, 256, 256, 5)])
 def test_expert_ffn_weights_as_m_against_oracle(world1, T, E, K, H, I, grid):
     """The grouped FFN with the weights as the M = 128 operand (gate/up + SwiGLU + down in one
     persistent launch): experts with no token, with a few, and with more than 256 (several passes
-    over the same weight block), more units than CTAs, interleaved gate/up rows."""
+    over the same weight block), more units than CTAs, interleaved gate/up rows; about 100 tokens per
+    expert (one block per pipeline stage, the next unit's gather indices fetched under the current one)."""
     from moe_comms_benchmarking_b200.ops import oracle
     from moe_comms_benchmarking_b200.ops.experts import ExpertFfnPlan, ExpertWeights, RouteBuffers, RoutePlan
     from moe_comms_benchmarking_b200.parallel.symm_heap import SymmetricHeap
