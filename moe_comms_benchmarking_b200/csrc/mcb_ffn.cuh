@@ -53,7 +53,8 @@ constexpr int kFfnABytes = kFfnRowsM * kFfnBlockK * 2;           // 16 KiB per 6
 constexpr int kFfnPipeBytes = 196 * 1024;
 constexpr int kFfnMaxExperts = 1024;        // local experts (their pair offsets are kept in shared memory)
 constexpr int kFfnOffBytes = (kFfnMaxExperts + 1) * 4 + 124;     // rounded to 128
-constexpr int kFfnSmemBytes = kFfnPipeBytes + 1024 /*align*/ + 512 /*barriers*/ + kFfnOffBytes;
+constexpr int kFfnEpiBytes = 4 * 1024;      // one 16 column x 32 feature bf16 transposition tile per epilogue warp
+constexpr int kFfnSmemBytes = kFfnPipeBytes + 1024 /*align*/ + 512 /*barriers*/ + kFfnOffBytes + kFfnEpiBytes;
 
 __device__ __forceinline__ int ld_acquire_gpu_i32(const int* p) {
   int v;
@@ -196,6 +197,10 @@ __device__ __forceinline__ void ffn_device_impl(const McbFfnArgs& a, const int n
   } else if (warp < 6) {
     // ---------------- epilogue: TMEM (lane = weight row, column = token) -> global ----------------
     const int q = warp & 3;                  // TMEM lane quarter this warp may read
+    // A lane holds ONE feature of 16 tokens, memory wants the features of a token side by side: the values
+    // cross a small tile in shared memory ([column][feature], 64 or 32 bytes per row) and leave as 16-byte
+    // stores, two (down) or one (gate/up) per 16 columns instead of sixteen or eight 2-byte ones.
+    uint8_t* tile = smem + kFfnPipeBytes + 512 + kFfnOffBytes + q * 1024;
     int acc = 0; uint32_t acc_ph = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
@@ -213,7 +218,7 @@ __device__ __forceinline__ void ffn_device_impl(const McbFfnArgs& a, const int n
             // rows alternate gate / up: lane pairs (2i, 2i + 1) hold the two halves of activation i
             const int feat = j * (kFfnRowsM / 2) + q * 16 + (lane >> 1);
             const bool odd = lane & 1;
-            uint8_t* obase = reinterpret_cast<uint8_t*>(a.act) + (long long)feat * 2;
+            uint8_t* obase0 = reinterpret_cast<uint8_t*>(a.act) + (long long)(feat - (lane >> 1)) * 2;   // first feature of the warp
 #pragma unroll 1
             for (int cc = 0; cc < n; cc += 16) {
               uint32_t v[16];
@@ -226,13 +231,19 @@ __device__ __forceinline__ void ffn_device_impl(const McbFfnArgs& a, const int n
                 const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
                 const float g = __uint_as_float(odd ? recv : v[i]);
                 const float up = __uint_as_float(odd ? v[8 + i] : recv);
-                const int col = cc + (odd ? 8 : 0) + i;
-                if (col < n) st_bf16(obase + (prow0 + col) * (long long)I * 2, silu(g) * up);
+                st_bf16(tile + ((odd ? 8 : 0) + i) * 32 + (lane >> 1) * 2, silu(g) * up);
               }
+              __syncwarp();
+              {   // 16 columns x 16 features: lane l stores half (l & 1) of column l >> 1
+                const int col = cc + (lane >> 1);
+                const uint4 w = *reinterpret_cast<const uint4*>(tile + (lane >> 1) * 32 + (lane & 1) * 16);
+                if (col < n) st_v4(obase0 + (prow0 + col) * (long long)I * 2 + (lane & 1) * 16, w);
+              }
+              __syncwarp();
             }
           } else {
             const int feat = j * kFfnRowsM + q * 32 + lane;
-            uint8_t* obase = reinterpret_cast<uint8_t*>(a.y) + (long long)feat * 2;
+            uint8_t* obase0 = reinterpret_cast<uint8_t*>(a.y) + (long long)(feat - lane) * 2;             // first feature of the warp
             // routing weights of the pass: lane l keeps those of columns l, l + 32, ... (one trip to L2 for the
             // whole pass instead of one per 16 columns), handed out by shuffles below
             float pp[kFfnMaxN / 32];
@@ -254,8 +265,16 @@ __device__ __forceinline__ void ffn_device_impl(const McbFfnArgs& a, const int n
               for (int i = 0; i < 16; ++i) {
                 const int col = cc + i;
                 const float p = __shfl_sync(0xffffffffu, mine, col & 31);
-                if (col < n) st_bf16(obase + (prow0 + col) * (long long)H * 2, __uint_as_float(v[i]) * p);
+                st_bf16(tile + i * 64 + lane * 2, __uint_as_float(v[i]) * p);
               }
+              __syncwarp();
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {   // 16 columns x 32 features: lane l stores quarter (l & 3) of column 8h + (l >> 2)
+                const int cl = 8 * h + (lane >> 2);
+                const uint4 w = *reinterpret_cast<const uint4*>(tile + cl * 64 + (lane & 3) * 16);
+                if (cc + cl < n) st_v4(obase0 + (prow0 + cc + cl) * (long long)H * 2 + (lane & 3) * 16, w);
+              }
+              __syncwarp();
             }
           }
         }
