@@ -105,3 +105,23 @@ def test_low_latency_limit_and_heap_sizing():
     specs = DenseDispatcher.heap_specs(cfg)
     assert specs[0][0] == [2, 8192, 1024] and len(specs) == 7     # gathered rows: two layer parities
     assert required_bytes(specs) > 8192 * (2 * (2048 + 176 + 88) + 2048)
+
+
+def test_all_to_all_packet_mode_limit_and_staging_sizes():
+    from moe_comms_benchmarking_b200.ops.a2a import a2a_ll_specs, a2a_ll_words, a2a_meta_row_bytes
+    from moe_comms_benchmarking_b200.parallel.a2a import A2ADispatcher, resolve_a2a_ll_rows
+    assert resolve_a2a_ll_rows(Config(ep_size=1, per_rank_cap=64), -1) == 0
+    assert resolve_a2a_ll_rows(Config(ep_size=8, per_rank_cap=1024), -1) == 1024
+    assert resolve_a2a_ll_rows(Config(ep_size=8, per_rank_cap=4), -1) == 32          # never above the capacity
+    assert resolve_a2a_ll_rows(Config(ep_size=2, per_rank_cap=4096), 0) == 0
+    # a dispatched token: header word + row words + (e4m3: two scales per word) + metadata words
+    meta = a2a_meta_row_bytes(22)
+    assert meta % 16 == 0 and meta >= 8 + 8 * 22
+    assert a2a_ll_words(1024, 22, False) == (1 + 256 + meta // 8, 256)
+    assert a2a_ll_words(1024, 22, True) == (1 + 128 + 4 + meta // 8, 256)
+    x, y, credits = a2a_ll_specs(8, 1024, 1024, 22, False, 256)
+    xw, yw = a2a_ll_words(1024, 22, False)
+    assert x[0] == [2 * 8 * 256 * xw * 16] and y[0] == [2 * 8 * 256 * yw * 16]       # two parities, one region per source
+    assert a2a_ll_specs(8, 1024, 1024, 22, False, 0) == [] and a2a_ll_specs(1, 64, 1024, 22, False, 256) == []
+    cfg = Config(ep_size=8, per_rank_cap=1024)
+    assert len(A2ADispatcher.heap_specs(cfg, False, 0)) + 3 == len(A2ADispatcher.heap_specs(cfg, False, 256))

@@ -71,3 +71,37 @@ def test_block_quant_error_bound(rows, blocks, scale):
     amax = x.view(rows, blocks, 128).abs().amax(-1)
     assert torch.allclose(s, torch.where(amax > 0, amax / 448, torch.ones_like(amax)))
     assert ((back - x).abs() <= 0.0625 * x.abs() + 2e-3 * s.repeat_interleave(128, dim=1)).all()
+
+
+def test_bench_child_job_csv_is_parsed(monkeypatch, tmp_path):
+    """bench.py times the expert path and the all-to-all dispatcher through run.py in a child job and reads
+    the child's CSV: the command line names the implementation and the batches, rows of other
+    implementations or phases are ignored, a failing child raises."""
+    import subprocess
+    import sys
+    import os
+    import pytest
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    seen = {}
+
+    def fake_run(cmd, **kw):
+        seen["cmd"] = cmd
+        out = cmd[cmd.index("--out") + 1]
+        with open(out, "w") as f:
+            f.write("impl,global_B,num_sms,phase,per_rank_counts,latency_us,timing\n")
+            f.write('a2a,1,148,decode_step,"[1, 0]",610.5,graph\n')
+            f.write('a2a,64,148,dispatch,"[32, 32]",5.0,graph\n')
+            f.write('dense,64,148,decode_step,"[32, 32]",590.0,graph\n')
+            f.write('a2a,64,148,decode_step,"[32, 32]",713.72,graph\n')
+        return subprocess.CompletedProcess(cmd, seen.get("rc", 0), "", "boom")
+
+    monkeypatch.setattr(subprocess, "run", fake_run)
+    ms = bench.run_child(2, "a2a", [1, 64], ["--reps", "10"])
+    assert ms == {"1": 0.6105, "64": 0.7137}
+    cmd = seen["cmd"]
+    assert cmd[cmd.index("--impl") + 1] == "a2a" and cmd[cmd.index("--batch-sizes") + 1] == "1,64"
+    assert cmd[cmd.index("--nproc-per-node") + 1] == "2" and "--reps" in cmd
+    seen["rc"] = 3
+    with pytest.raises(RuntimeError):
+        bench.run_child(2, "a2a", [1], [])
