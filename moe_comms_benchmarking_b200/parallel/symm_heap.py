@@ -73,11 +73,13 @@ class SymmetricHeap:
     """``SymmetricHeap(group, nbytes, device)`` is collective over ``group``."""
 
     def __init__(self, group, nbytes: int, device, transport: str = "auto", timeout_s: float = 2.0,
-                 multicast: bool = True):
+                 multicast: bool = True, allocator: str | None = None):
         """``multicast=False`` keeps the allocation out of any NVSwitch multicast object (peer
         mappings only).  Jobs in which a rank may leave while others keep running must use it: a
         rank that disappears while its memory is bound to a multicast object can raise NVLink
-        faults on the surviving GPUs."""
+        faults on the surviving GPUs.  ``allocator``: ``"torch"`` (PyTorch's symmetric memory, the
+        default) or ``"native"`` (this library's own allocator on the driver's virtual-memory API,
+        ``parallel/native_heap.py``; one node); ``None`` reads ``MCB_HEAP_ALLOCATOR``."""
         self.group = group
         self.multicast = bool(multicast)
         self.device = torch.device(device)
@@ -93,8 +95,15 @@ class SymmetricHeap:
         self._site_grid: dict[int, int] = {}
         self.peer_ptrs = [0] * self.world
         self.mc_ptr = 0
+        self._native = None
+        allocator = allocator or os.environ.get("MCB_HEAP_ALLOCATOR", "torch")
+        if allocator not in ("torch", "native"):
+            raise ValueError(f"unknown heap allocator {allocator!r}")
+        self.allocator = allocator
         on_gpu = self.device.type == "cuda"
-        if self.world > 1 and on_gpu:
+        if self.world > 1 and on_gpu and allocator == "native":
+            self._init_native()
+        elif self.world > 1 and on_gpu:
             self._init_torch_symm()
         else:
             # World of one, or CPU ranks: an ordinary allocation is "symmetric" trivially.
@@ -148,6 +157,21 @@ class SymmetricHeap:
             self.init_failure_reason = f"{type(e).__name__}: {e}"
             raise RuntimeError(f"symmetric heap bring-up failed: {self.init_failure_reason}") from e
 
+    def _init_native(self):
+        from .native_heap import NativeHeapBackend
+        try:
+            self._native = NativeHeapBackend(self.group, self.nbytes, self.device, multicast=self.multicast)
+        except Exception as e:
+            self.init_failure_reason = f"{type(e).__name__}: {e}"
+            raise RuntimeError(f"symmetric heap bring-up failed: {self.init_failure_reason}") from e
+        self.nbytes = self._native.nbytes
+        self.buffer = self._native.buffer
+        self.peer_ptrs = list(self._native.peer_ptrs)
+        self.mc_ptr = self._native.mc_ptr
+        if not self.mc_ptr:
+            self.init_failure_reason = ("multicast disabled on request" if not self.multicast
+                                        else "the devices of this group do not support multicast objects")
+
     # -- sub-allocation -----------------------------------------------------------------------
     def alloc(self, key: str, shape, dtype) -> HeapTensor:
         """Carve ``shape`` x ``dtype`` out of the heap under ``key``.  Every rank must call this
@@ -199,6 +223,12 @@ class SymmetricHeap:
         """This rank's mapping of ``peer``'s copy of a heap tensor (debug / validation only)."""
         if peer == self.rank:
             return ht.tensor
+        if self._native is not None:
+            from .native_heap import _RawCudaBytes
+            raw = _RawCudaBytes(self.peer_ptrs[peer] + ht.offset, ht.nbytes)
+            t = torch.as_tensor(raw, device=self.device)
+            t._mcb_keepalive = raw
+            return t.view(ht.tensor.dtype).view(tuple(ht.tensor.shape))
         if self._handle is None:
             raise RuntimeError("no peer mappings on this heap")
         esize = ht.tensor.element_size()
@@ -281,10 +311,14 @@ class SymmetricHeap:
             dist.barrier(self.group)
 
     def destroy(self):
+        """With the native allocator this is collective (the mappings of the peers go away)."""
         self._registry.clear()
         self._reset_hooks.clear()
         self._handle = None
         self.buffer = None
+        if self._native is not None:
+            self._native.close()
+            self._native = None
 
 
 class SymmetricHeapManager:

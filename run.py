@@ -239,7 +239,7 @@ def main(argv=None) -> int:
             b.build()
         dist.barrier(group)
     if rank == 0 and heap is not None:
-        say(f"# symmetric heap: {heap.bytes_used() / 2**20:.1f} MiB used, transport={heap.transport}")
+        say(f"# symmetric heap: {heap.bytes_used() / 2**20:.1f} MiB used, transport={heap.transport}, allocator={heap.allocator}")
 
     if args.validate:
         local_ok = True

@@ -148,3 +148,20 @@ def test_rank_leaving_between_steps_is_seen_on_the_host(tmp_path):
     if "MULTICAST_STILL_BOUND" in out:
         pytest.skip("this PyTorch binds a multicast object regardless; a rank departure is not exercised on GPUs")
     assert "rank 0 saw rank(s) [1] left the job" in out, out[-4000:]
+
+
+def test_native_heap_allocator_multi_gpu():
+    """The library's own symmetric-heap allocator (driver virtual-memory API, descriptors over unix sockets,
+    one multicast object) under both dispatchers and the tensor-parallel collectives: the same checks as with
+    PyTorch's allocator, and the heap must have a multicast address of its own."""
+    n = _ngpu()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    n = 4 if n >= 4 else 2
+    env = {"MCB_HEAP_ALLOCATOR": "native"}
+    res = _torchrun(n, ["run.py", "--impl", "both", "--validate"], env=env)
+    assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-4000:]
+    assert f"# VALIDATION PASSED (all {n} ranks)" in res.stdout
+    res = _torchrun(n, ["-m", "moe_comms_benchmarking_b200.selftest"], env=env)
+    assert res.returncode == 0, res.stdout[-4000:] + res.stderr[-4000:]
+    assert f"# SELFTEST PASSED (all {n} ranks, transport=multimem" in res.stdout
