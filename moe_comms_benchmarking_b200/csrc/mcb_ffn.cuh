@@ -36,6 +36,10 @@
 //     done" counter) are requested while the current unit is still being copied; the routing weights of a
 //     pass are fetched once per pass and handed to the epilogue's stores by shuffles.  (With these trips to
 //     L2 on the critical path the pipeline drained at every unit: 147.7 -> 128.6 us at 4096 gathered tokens.)
+//   * the epilogue reads the accumulators with tcgen05.ld (a lane holds ONE output feature of 16 tokens),
+//     turns them through a small shared-memory tile and stores 16 bytes per lane, feature-contiguous as
+//     the next GEMM and the combine want them (2-byte stores made the epilogue the slowest role from a
+//     few thousand tokens on: 128.4 -> 111.7 us at 4096 gathered tokens);
 //   * one elected thread issues tcgen05.mma; every mbarrier wait is bounded and reports through the
 //     status words.
 #pragma once
