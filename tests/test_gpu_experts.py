@@ -261,3 +261,30 @@ def test_layer_kernel_fused_dispatcher_world1(world1):
     s = float(ref.abs().max())
     assert float((d.out.float().cpu() - ref).abs().max()) < 0.05 * s
     d.destroy()
+
+
+def test_layer_kernel_phase_trace_world1(world1):
+    """The optional device trace of the layer kernel: seven phases in order, none negative, together no
+    longer than the step they belong to; and the traced layer still computes the right rows."""
+    from moe_comms_benchmarking_b200.config import Config
+    from moe_comms_benchmarking_b200.parallel.fused import FusedExpertDispatcher
+    from moe_comms_benchmarking_b200.utils.inputs import make_inputs
+    cfg = Config(num_experts=16, topk=4, hidden=512, intermediate=256, ep_size=1, per_rank_cap=96)
+    d = FusedExpertDispatcher(cfg, world1, num_layers=1, weight_budget_gb=1.0, phase_trace=True)
+    d.build()
+    h, i, w = make_inputs(cfg, 80, DEV)
+    d.setup_batch(h, i, w)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    d.decode_step(1)                       # warm-up
+    torch.cuda.synchronize()
+    t0.record(); d.decode_step(1); t1.record()
+    torch.cuda.synchronize()
+    d.check_health()
+    phases = d.layer_plan.phase_times()
+    assert [n for n, _ in phases] == ["dispatch", "grid barrier", "routing", "grid barrier", "experts", "grid barrier", "combine"]
+    assert all(us >= 0 for _, us in phases)
+    total = sum(us for _, us in phases)
+    assert 0 < total <= t0.elapsed_time(t1) * 1e3 + 50.0
+    ref = d.reference_output(h, i, w, layer=0)
+    assert float((d.out.float().cpu() - ref).abs().max()) < 0.05 * float(ref.abs().max())
+    d.destroy()
