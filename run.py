@@ -83,6 +83,9 @@ def parse_args(argv=None):
                    help="fused: the two-kernel form with tokens as the M operand instead of one kernel per layer")
     p.add_argument("--dense-num-sms", type=int, default=148, help="CTA cap of the dense kernels")
     p.add_argument("--transport", choices=["auto", "multimem", "p2p"], default="auto")
+    p.add_argument("--heap-allocator", choices=["torch", "native"], default=None,
+                   help="host-side allocator of the symmetric heap: PyTorch's symmetric memory (default) or this "
+                        "library's own (driver virtual-memory API, one node); default: $MCB_HEAP_ALLOCATOR or torch")
     p.add_argument("--ll-rows", type=int, default=-1,
                    help="dense dispatcher: steps with at most this many tokens over all ranks use "
                         "low-latency flagged packets instead of barrier + multicast (0 = never, -1 = measured default)")
@@ -212,6 +215,8 @@ def cross_impl_check(benchers, cfg, world, rank, device, say):
 
 def main(argv=None) -> int:
     args = parse_args(argv)
+    if args.heap_allocator:
+        os.environ["MCB_HEAP_ALLOCATOR"] = args.heap_allocator       # every heap of this job follows
     group, rank, world, local_rank = init_distributed()
     on_gpu = torch.cuda.is_available()
     device = torch.device("cuda", local_rank) if on_gpu else torch.device("cpu")
