@@ -56,6 +56,19 @@ def test_multimem_transport_needs_multicast():
         SymmetricHeap(None, 1 << 16, "cpu", transport="multimem")
 
 
+def test_heap_allocator_choice(monkeypatch):
+    """The allocator is a named choice (argument first, then the environment); a CPU heap or a world of one
+    needs none of them, whatever is asked for."""
+    with pytest.raises(ValueError):
+        SymmetricHeap(None, 1 << 16, "cpu", allocator="cudamalloc")
+    h = SymmetricHeap(None, 1 << 16, "cpu", allocator="native")
+    assert h.allocator == "native" and h.buffer.device.type == "cpu" and h.mc_ptr == 0
+    monkeypatch.setenv("MCB_HEAP_ALLOCATOR", "native")
+    assert SymmetricHeap(None, 1 << 16, "cpu").allocator == "native"
+    monkeypatch.delenv("MCB_HEAP_ALLOCATOR")
+    assert SymmetricHeap(None, 1 << 16, "cpu").allocator == "torch"
+
+
 def test_status_error_decoding():
     e = DeviceStatusError([1, 2, 7, 5, 8, 3, 0, 0])
     assert e.code == 1 and "timeout" in str(e) and "site 2 block 7 on rank 3" in str(e)
